@@ -1,0 +1,94 @@
+"""Tiny LFM2 configurations for the tests and helpers to build, replay and compare them.
+
+tiny_a and tiny_b are the two configurations that differ in every size and option (first layer
+kind, head counts and group size, head size, feed-forward rule, conv window and bias, rope
+base, eps, tied or untied head, norm-weight init, vocabulary); tiny_c adds a windowed
+attention group next to a full one, a width and vocabulary that are no power of two, a
+two-tap convolution and a float32 weight file.
+"""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[1]
+
+TINY = {
+    "tiny_a": dict(
+        config=dict(architectures=["Lfm2ForCausalLM"], model_type="lfm2", vocab_size=256, hidden_size=64,
+                    num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                    layer_types=["conv", "full_attention", "conv", "full_attention"], block_ff_dim=128,
+                    block_auto_adjust_ff_dim=False, conv_L_cache=3, conv_bias=False, rope_theta=10000.0,
+                    norm_eps=1e-5, tie_word_embeddings=True, eos_token_id=7),
+        seed=11, norm_init="one_plus_normal", storage="bfloat16"),
+    "tiny_b": dict(
+        config=dict(architectures=["Lfm2ForCausalLM"], model_type="lfm2", vocab_size=512, hidden_size=96,
+                    num_hidden_layers=6, num_attention_heads=3, num_key_value_heads=1, max_position_embeddings=256,
+                    layer_types=["full_attention", "conv", "conv", "full_attention", "conv", "full_attention"],
+                    block_ff_dim=288, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0,
+                    block_multiple_of=64, conv_L_cache=4, conv_bias=True, rope_theta=1000000.0, norm_eps=1e-6,
+                    tie_word_embeddings=False, eos_token_id=[3, 5]),
+        seed=23, norm_init="normal", storage="bfloat16"),
+    "tiny_c": dict(
+        config=dict(architectures=["Lfm2ForCausalLM"], model_type="lfm2", vocab_size=331, hidden_size=80,
+                    num_hidden_layers=5, num_attention_heads=5, num_key_value_heads=5, head_dim=48,
+                    max_position_embeddings=512,
+                    layer_types=["sliding_attention", "conv", "full_attention", "sliding_attention", "conv"],
+                    sliding_window=24, block_ff_dim=200, block_auto_adjust_ff_dim=True, block_multiple_of=8,
+                    conv_L_cache=2, conv_bias=False, rope_theta=50000.0, norm_eps=3e-6,
+                    tie_word_embeddings=True, eos_token_id=2),
+        seed=37, norm_init="one_plus_normal", storage="float32"),
+}
+
+
+def make_model_folder(folder, name: str) -> Path:
+    import torch
+    import zinfer_b200 as z
+
+    spec = TINY[name]
+    cfg = z.config_from_dict(spec["config"])
+    return z.write_random_model(folder, cfg, spec["seed"], norm_init=spec["norm_init"],
+                                storage_dtype=getattr(torch, spec["storage"]))
+
+
+def random_tokens(seed: int, n: int, vocab: int) -> list[int]:
+    return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
+
+
+def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
+    """Largest absolute difference relative to the largest reference magnitude."""
+    scale = float(np.max(np.abs(ref)))
+    assert scale > 0, "reference logits are all zero: the comparison would be empty"
+    return float(np.max(np.abs(got.astype(np.float64) - ref.astype(np.float64)))) / scale
+
+
+# tolerances, relative to max |logit| of the plain implementation
+TOL = {"float32": 5e-5, "bfloat16": 2e-2}
+
+
+def run_trace(model_dir, dtype: str, steps: list[dict], max_tokens: int, out_dir) -> dict[int, np.ndarray]:
+    """Runs bin/trace_run on `steps`; returns step -> float32 array [wanted, vocab]."""
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    proc = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out",
+                           str(out_dir), "--max-tokens", str(max_tokens)], input=text, capture_output=True, text=True,
+                          timeout=900, env=dict(os.environ, ZINFER_PYTHON=sys.executable))
+    assert proc.returncode == 0, f"trace_run failed ({proc.returncode}):\n{proc.stdout[-2000:]}\n{proc.stderr[-4000:]}"
+    done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
+    assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps], proc.stdout[-2000:]
+    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    out = {}
+    for s in steps:
+        f = out_dir / f"{s['step']}.f32"
+        wanted = sum(len(e.get("want", [])) for e in s["entries"])
+        if wanted:
+            out[s["step"]] = np.fromfile(f, dtype="<f4").reshape(wanted, vocab)
+        else:
+            assert not f.exists()
+    return out

@@ -1,0 +1,325 @@
+"""Each kernel alone against a plain float64 reference, at sizes other than the tiny models':
+widths and vocabularies that are no power of two, head sizes in steps of 16, odd group sizes,
+page edges, and inputs made so that a fault shows (one far key that must win the softmax, a
+window's edge)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.5e-2
+
+
+def close(got, ref, dtype, what=""):
+    got = got.detach().double().cpu()
+    ref = ref.detach().double().cpu()
+    scale = ref.abs().max().item()
+    assert scale > 0, f"{what}: empty reference"
+    err = (got - ref).abs().max().item() / scale
+    assert err <= tol(dtype), f"{what}: error {err:.3e} of max |ref| {scale:.3e}"
+
+
+def rnd(shape, seed, dtype, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.fixture(scope="module")
+def k():
+    from zinfer_b200 import kernels
+    kernels.require_cuda()
+    return kernels
+
+
+# ------------------------------------------------------------------------------- row kernels
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim", [48, 2048 + 16, 7])
+def test_embed_and_status(k, dtype, dim):
+    vocab = 331
+    table = rnd((vocab, dim), 1, dtype).cuda()
+    toks = torch.tensor([0, 330, 17, 5, 17], dtype=torch.int32).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    x = k.embed(toks, table, status)
+    assert x.dtype == torch.float32 and status.item() == 0
+    assert torch.equal(x.cpu(), table.float().cpu()[toks.cpu().long()])
+    bad = torch.tensor([3, vocab], dtype=torch.int32).cuda()
+    x = k.embed(bad, table, status)
+    assert status.item() == 1 and x[1].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,dim,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (2, 1000, 3e-6), (1, 16, 1e-5)])
+def test_rmsnorm(k, dtype, n, dim, eps):
+    x = rnd((n, dim), 2, torch.float32, 3.0).cuda()
+    w = (1 + rnd((dim,), 3, torch.float32, 0.1)).cuda()
+    ref = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * w.double()
+    close(k.rmsnorm(x, w, eps, dtype), ref, dtype, "rmsnorm")
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32).cuda()
+    close(k.rmsnorm(x, w, eps, dtype, rows), ref[[n - 1, 0]], dtype, "rmsnorm rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(k, dtype):
+    n, F = 7, 200
+    gu = rnd((n, 2 * F), 4, dtype, 2.0).cuda()
+    g, u = gu[:, :F].double(), gu[:, F:].double()
+    close(k.silu_mul(gu), g / (1 + torch.exp(-g)) * u, dtype, "silu_mul")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (5, 64, 64), (70, 200, 96), (130, 257, 1000), (64, 128, 2048)])
+def test_gemm_simt(k, dtype, M, N, K):
+    a = rnd((M, K), 5, dtype).cuda()
+    w = rnd((N, K), 6, dtype, 0.1).cuda()
+    bias = rnd((N,), 7, torch.float32).cuda()
+    ref = a.double() @ w.double().T
+    close(k.gemm_simt(a, w), ref, dtype, "gemm")
+    close(k.gemm_simt(a, w, out_dtype=torch.float32), ref, dtype, "gemm f32 out")
+    close(k.gemm_simt(a, w, bias=bias, out_dtype=torch.float32), ref + bias.double(), dtype, "gemm bias")
+    res = rnd((M, N), 8, torch.float32).cuda()
+    res0 = res.clone()
+    k.gemm_simt(a, w, out=res, accumulate=True)
+    close(res, ref + res0.double(), dtype, "gemm accumulate")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
+    """A row's contraction is the same bits alone, in a batch, and at another place of it."""
+    from zinfer_b200.parts.linear import linear
+    a = rnd((70, 96), 9, dtype).cuda()
+    w = rnd((200, 96), 10, dtype, 0.1).cuda()
+    full = linear(a, w, out_dtype=torch.float32)
+    one = linear(a[33:34].contiguous(), w, out_dtype=torch.float32)
+    moved = linear(a[30:40].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(full[33], one[0]) and torch.equal(full[33], moved[3])
+
+
+# ------------------------------------------------------------------------------- short convolution
+
+def conv_ref(bcx, taps, bias, state):
+    """bcx [T, 3D] of one sequence, taps [K, D], state [K-1, D] -> (y [T, D], new state)."""
+    T, D = bcx.shape[0], bcx.shape[1] // 3
+    K = taps.shape[0]
+    u = bcx[:, :D] * bcx[:, 2 * D:]
+    hist = torch.cat([state, u], 0)
+    c = torch.zeros(T, D, dtype=torch.float64)
+    for j in range(K):
+        c += taps[j] * hist[j:j + T]
+    if bias is not None:
+        c += bias
+    return bcx[:, D:2 * D] * c, hist[T:]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D,K,use_bias", [(80, 2, False), (96, 4, True), (200, 3, False), (64, 7, True)])
+def test_short_conv_packed_and_stepwise(k, dtype, D, K, use_bias):
+    lens = [1, 2, 9, K - 1, 33]
+    slots = [4, 0, 2, 5, 1]
+    n_slots = 6
+    taps = rnd((K, D), 11, torch.float32).cuda()
+    bias = rnd((D,), 12, torch.float32).cuda() if use_bias else None
+    seqs = [rnd((l, 3 * D), 20 + i, dtype) for i, l in enumerate(lens)]
+    state = rnd((n_slots, K - 1, D), 13, torch.float32).cuda()     # junk in every slot ...
+    state[slots] = 0                                               # ... but zero where a sequence starts
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    tok_seq = torch.from_numpy(np.repeat(np.arange(len(lens)), lens).astype(np.int32)).cuda()
+    cu_q = torch.from_numpy(cu).cuda()
+    seq_slot = torch.tensor(slots, dtype=torch.int32).cuda()
+    bcx = torch.cat(seqs).cuda()
+    y = k.conv_forward(bcx, state, taps, bias, tok_seq, cu_q, seq_slot)
+    k.conv_state_update(bcx, state, cu_q, seq_slot, len(lens), K)
+    refs = [conv_ref(s.double(), taps.double().cpu(), None if bias is None else bias.double().cpu(),
+                     torch.zeros(K - 1, D, dtype=torch.float64)) for s in seqs]
+    close(y, torch.cat([r[0] for r in refs]), dtype, "conv prefill y")
+    for s, r in zip(slots, refs):
+        close(state[s], r[1], torch.float32, "conv state after prefill") if r[1].abs().max() > 0 else None
+    assert torch.equal(state[3].cpu(), rnd((n_slots, K - 1, D), 13, torch.float32)[3]), "a slot not in the batch changed"
+    # three more single-token steps for every sequence, compared with the whole sequence at once
+    more = [rnd((3, 3 * D), 40 + i, dtype) for i in range(len(lens))]
+    for t in range(3):
+        step = torch.stack([m[t] for m in more]).cuda()
+        yd = k.conv_decode(step, state, taps, bias, seq_slot)
+        for i in range(len(lens)):
+            whole = conv_ref(torch.cat([seqs[i], more[i][:t + 1]]).double(), taps.double().cpu(),
+                             None if bias is None else bias.double().cpu(), torch.zeros(K - 1, D, dtype=torch.float64))
+            close(yd[i], whole[0][-1], dtype, f"conv decode step {t} seq {i}")
+    # a second packed step (continuation of a prompt) must equal the decode path
+    state2 = torch.zeros_like(state)
+    k.conv_state_update(bcx, state2, cu_q, seq_slot, len(lens), K)
+    cont = torch.cat(more).cuda()
+    cu2 = torch.from_numpy(np.arange(0, 3 * len(lens) + 1, 3).astype(np.int32)).cuda()
+    ts2 = torch.from_numpy(np.repeat(np.arange(len(lens)), 3).astype(np.int32)).cuda()
+    y2 = k.conv_forward(cont, state2, taps, bias, ts2, cu2, seq_slot)
+    for i in range(len(lens)):
+        whole = conv_ref(torch.cat([seqs[i], more[i]]).double(), taps.double().cpu(),
+                         None if bias is None else bias.double().cpu(), torch.zeros(K - 1, D, dtype=torch.float64))
+        close(y2[3 * i:3 * i + 3], whole[0][-3:], dtype, f"conv continued prompt seq {i}")
+
+
+# ------------------------------------------------------------------------------- attention
+
+def rope_ref(x, pos, inv_freq, interleaved=False):
+    """x [T, heads, hd] float64; NeoX or interleaved pairing."""
+    half = inv_freq.shape[0]
+    ang = (pos.float()[:, None] * inv_freq.float()[None, :]).double()
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:2 * half:2], x[..., 1:2 * half:2]
+        out[..., 0:2 * half:2] = a * cos - b * sin
+        out[..., 1:2 * half:2] = a * sin + b * cos
+    else:
+        a, b = x[..., :half], x[..., half:2 * half]
+        out[..., :half] = a * cos - b * sin
+        out[..., half:2 * half] = a * sin + b * cos
+    return out
+
+
+def attn_ref(q, kk, v, starts_q, window, scale):
+    """q [Tq, H, hd] at positions starts_q.., keys kk, v [Tk, Hkv, hd] at positions 0..Tk-1."""
+    Tq, H, hd = q.shape
+    Hkv = kk.shape[1]
+    g = H // Hkv
+    out = torch.zeros_like(q)
+    for h in range(H):
+        s = (q[:, h] @ kk[:, h // g].T) * scale
+        i = (starts_q + torch.arange(Tq))[:, None]
+        j = torch.arange(kk.shape[0])[None, :]
+        mask = j <= i
+        if window > 0:
+            mask &= j >= i + 1 - window
+        s = s.masked_fill(~mask, float("-inf"))
+        out[:, h] = torch.softmax(s, -1) @ v[:, h // g]
+    return out
+
+
+class PagedSetup:
+    """A small paged cache with shuffled pages for sequences of given lengths."""
+
+    def __init__(self, lens, slots, n_slots, page_size, Hkv, hd, dtype, seed=0):
+        self.page_size = page_size
+        pages_per = [-(-l // page_size) for l in lens]
+        n_pages = sum(pages_per) + 3
+        perm = np.random.default_rng(seed).permutation(n_pages)
+        self.table = np.full((n_slots, max(pages_per) + 1), -1, dtype=np.int32)
+        it = iter(perm)
+        for s, n in zip(slots, pages_per):
+            for i in range(n):
+                self.table[s, i] = next(it)
+        self.k = torch.full((n_pages, Hkv, page_size, hd), float("nan"), dtype=dtype).cuda()
+        self.v = torch.full((n_pages, Hkv, page_size, hd), float("nan"), dtype=dtype).cuda()
+        self.table_dev = torch.from_numpy(self.table).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Hkv,hd,page,n_rot,inter", [(4, 2, 16, 16, 16, False), (3, 1, 32, 32, 32, False),
+                                                       (5, 5, 48, 64, 48, False), (8, 2, 80, 16, 40, True),
+                                                       (6, 2, 128, 64, 128, False), (20, 1, 64, 32, 64, False)])
+def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
+    """Prompt step of unequal lengths into NaN-filled shuffled pages, then a single-token step
+    with and without key splits, against whole-sequence references."""
+    from zinfer_b200.engine.context import attn_tiles_host
+    lens = [1, 2, 37, 70, 5]
+    slots = [3, 0, 5, 1, 4]
+    eps = 1e-5
+    scale = 1 / math.sqrt(hd)
+    setup = PagedSetup([l + 1 for l in lens], slots, 6, page, Hkv, hd, dtype)
+    qw = (1 + rnd((hd,), 1, torch.float32, 0.1)).cuda()
+    kw = (1 + rnd((hd,), 2, torch.float32, 0.1)).cuda()
+    inv_freq = torch.from_numpy(np.power(10000.0, -2.0 * np.arange(n_rot // 2) / n_rot).astype(np.float32)).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    width = (H + 2 * Hkv) * hd
+    seqs = [rnd((l + 1, width), 50 + i, dtype) for i, l in enumerate(lens)]   # last row = the decode token
+
+    def reference(i, upto):
+        x = seqs[i][:upto].double()
+        q = x[:, :H * hd].reshape(upto, H, hd)
+        kk = x[:, H * hd:(H + Hkv) * hd].reshape(upto, Hkv, hd)
+        v = x[:, (H + Hkv) * hd:].reshape(upto, Hkv, hd)
+        nrm = lambda t, w: t / torch.sqrt((t ** 2).mean(-1, keepdim=True) + eps) * w.double().cpu()
+        pos = torch.arange(upto)
+        q = rope_ref(nrm(q, qw), pos, inv_freq.cpu(), inter)
+        kk = rope_ref(nrm(kk, kw), pos, inv_freq.cpu(), inter)
+        if dtype == torch.bfloat16:      # the cache and q hold bfloat16
+            q, kk, v = q.bfloat16().double(), kk.bfloat16().double(), v.bfloat16().double()
+        return q, kk, v
+
+    def run(step_lens, starts, rows, num_splits=1, split_keys=0):
+        cu = np.concatenate([[0], np.cumsum(step_lens)]).astype(np.int32)
+        tok_seq = torch.from_numpy(np.repeat(np.arange(len(step_lens)), step_lens).astype(np.int32)).cuda()
+        tok_pos = torch.from_numpy(np.concatenate([np.arange(s, s + l) for s, l in zip(starts, step_lens)]).astype(np.int32)).cuda()
+        seq_slot = torch.tensor(slots, dtype=torch.int32).cuda()
+        seq_start = torch.tensor(starts, dtype=torch.int32).cuda()
+        cu_q = torch.from_numpy(cu).cuda()
+        q = k.qk_prepare(rows.cuda(), setup.k, setup.v, qw, kw, inv_freq, tok_seq, tok_pos, seq_slot, setup.table_dev,
+                         H, Hkv, hd, n_rot, inter, eps, status)
+        bq, _ = k.attn_tile_shape(H, Hkv)
+        tiles = torch.from_numpy(attn_tiles_host(step_lens, bq)).cuda()
+        return k.attention(q, setup.k, setup.v, tiles[0].contiguous(), tiles[1].contiguous(), cu_q, seq_start,
+                           seq_slot, setup.table_dev, H, Hkv, hd, scale, 0, num_splits, split_keys)
+
+    out = run(lens, [0] * len(lens), torch.cat([s[:-1] for s in seqs]))
+    assert status.item() == 0
+    ref = []
+    for i, l in enumerate(lens):
+        q, kk, v = reference(i, l)
+        ref.append(attn_ref(q, kk, v, 0, 0, scale).reshape(l, H * hd))
+    close(out, torch.cat(ref), dtype, "prefill attention")
+    last = torch.stack([s[-1] for s in seqs])
+    ref = []
+    for i, l in enumerate(lens):
+        q, kk, v = reference(i, l + 1)
+        ref.append(attn_ref(q[-1:], kk, v, l, 0, scale).reshape(1, H * hd))
+    ref = torch.cat(ref)
+    close(run([1] * len(lens), lens, last), ref, dtype, "decode attention")
+    close(run([1] * len(lens), lens, last, num_splits=3, split_keys=32), ref, dtype, "decode attention, 3 key chunks")
+    assert not torch.isnan(out).any()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 24, 64])
+def test_attention_far_key_and_window_edge(k, dtype, window):
+    """One key among hundreds is made to win the softmax; with a window the winner sits exactly
+    on the window's first position for one query and one position outside it for the next."""
+    from zinfer_b200.engine.context import attn_tiles_host
+    H, Hkv, hd, page = 4, 2, 32, 16
+    T = 300
+    scale = 1 / math.sqrt(hd)
+    far = 7 if window == 0 else T - 2 - window + 1     # position of the key that must win
+    kk = rnd((T, Hkv, hd), 1, dtype, 0.3)
+    v = rnd((T, Hkv, hd), 2, dtype)
+    q = rnd((T, H, hd), 3, dtype, 0.3)
+    kk[far] = 0
+    kk[far, :, 0] = 12.0
+    q[:, :, 0] = 12.0               # every query scores 144 * scale on the far key
+    setup = PagedSetup([T], [2], 4, page, Hkv, hd, dtype, seed=3)
+    pages = torch.from_numpy(setup.table[2, :-(-T // page)].astype(np.int64)).cuda()
+    pad = (-T) % page
+    kp = torch.cat([kk, torch.zeros(pad, Hkv, hd, dtype=dtype)]).reshape(-1, page, Hkv, hd).permute(0, 2, 1, 3)
+    vp = torch.cat([v, torch.zeros(pad, Hkv, hd, dtype=dtype)]).reshape(-1, page, Hkv, hd).permute(0, 2, 1, 3)
+    setup.k[pages] = kp.cuda()
+    setup.v[pages] = vp.cuda()
+    # the last two queries as one step continuing at position T-2
+    starts = T - 2
+    bq, _ = k.attn_tile_shape(H, Hkv)
+    tiles = torch.from_numpy(attn_tiles_host([2], bq)).cuda()
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    out = k.attention(q[-2:].reshape(2, H * hd).cuda(), setup.k, setup.v, tiles[0].contiguous(),
+                      tiles[1].contiguous(), i32([0, 2]), i32([starts]), i32([2]), setup.table_dev, H, Hkv, hd, scale,
+                      window)
+    ref = attn_ref(q[-2:].double(), kk.double(), v.double(), starts, window, scale).reshape(2, H * hd)
+    close(out, ref, dtype, f"far key, window {window}")
+    g = H // Hkv
+    won = torch.allclose(out[0].float().cpu().reshape(H, hd), v[far].float()[[h // g for h in range(H)]], atol=0.05)
+    assert won, "the far key did not win for the query that sees it"
+    if window:
+        lost = torch.allclose(out[1].float().cpu().reshape(H, hd), v[far].float()[[h // g for h in range(H)]], atol=0.05)
+        assert not lost, "a key outside the window was seen"

@@ -1,0 +1,103 @@
+// Row-wise kernels: embedding gather, RMSNorm (with optional row gather), SiLU-gate product.
+// All arithmetic is float32; only loads and stores use the run dtype.
+#include "common.cuh"
+
+// x[t, :] = float(table[tokens[t], :]).  A token id outside [0, vocab) sets *status = 1 and
+// yields a zero row (reference: row lookup of token_embd, src/model.zig:2352-2358).
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x,
+                             int dim, int vocab, float scale, int* status) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  if (!ok && threadIdx.x == 0) atomicExch(status, 1);
+  const T* row = table + (size_t)(ok ? tok : 0) * dim;
+  float* out = x + (size_t)t * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) out[d] = ok ? to_f32(row[d]) * scale : 0.f;
+}
+
+// y[r, :] = (x[src(r), :] * rsqrt(mean(x^2) + eps)) * w   (src/model.zig:1166-1181: scale
+// first, weight second).  src(r) = rows ? rows[r] : r.  One block per output row.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                               TO* __restrict__ y, int dim, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float v = xr[d];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+  TO* yr = y + (size_t)r * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) yr[d] = from_f32<TO>((xr[d] * scale) * w[d]);
+}
+
+// h[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(g) = g / (1 + exp(-g))
+// (src/ffn.zig:31-33, 49-57).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int n, int F) {
+  const size_t total = (size_t)n * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / F, f = i - t * F;
+    const float g = to_f32(gu[t * 2 * F + f]);
+    const float u = to_f32(gu[t * 2 * F + F + f]);
+    h[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+extern "C" {
+
+// Name of a status returned by any zk_* launcher (a cudaError_t value, or ZK_EINVAL).
+const char* zk_error_name(int code) {
+  if (code == ZK_EINVAL) return "ZK_EINVAL (a size or dtype the kernel does not take)";
+  return cudaGetErrorName((cudaError_t)code);
+}
+
+int zk_embed(const int* tokens, const void* table, float* x, int n, int dim, int vocab, float scale, int dtype,
+             int* status, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dim <= 0 || vocab <= 0) return ZK_EINVAL;
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (dtype == ZK_F32)
+    embed_kernel<float><<<n, threads, 0, stream>>>(tokens, (const float*)table, x, dim, vocab, scale, status);
+  else if (dtype == ZK_BF16)
+    embed_kernel<bf16><<<n, threads, 0, stream>>>(tokens, (const bf16*)table, x, dim, vocab, scale, status);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
+
+int zk_rmsnorm(const float* x, const int* rows, const float* w, void* y, int n_out, int dim, float eps, int out_dtype,
+               cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (dim <= 0) return ZK_EINVAL;
+  int threads = 32;
+  while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  if (out_dtype == ZK_F32)
+    rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(x, rows, w, (float*)y, dim, eps);
+  else if (out_dtype == ZK_BF16)
+    rmsnorm_kernel<bf16><<<n_out, threads, 0, stream>>>(x, rows, w, (bf16*)y, dim, eps);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
+
+int zk_silu_mul(const void* gu, void* h, int n, int F, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (F <= 0) return ZK_EINVAL;
+  const size_t total = (size_t)n * F;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == ZK_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)h, n, F);
+  else if (dtype == ZK_BF16)
+    silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)h, n, F);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
+
+}  // extern "C"

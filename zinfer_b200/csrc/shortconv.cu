@@ -1,0 +1,149 @@
+// Gated short convolution over a packed batch of sequences with per-slot state.
+//
+// bcx[t] = [B_t, C_t, X_t] (3*D values), u_t = B_t * X_t,
+// c_t[ch] = sum_{k=0}^{K-1} w[k][ch] * u_{t-(K-1)+k}[ch]  (+ bias[ch]),   y_t = C_t * c_t,
+// with u before the first token of this step taken from the slot's state (the last K-1
+// values of u of the sequence, oldest first) -- src/model.zig:1994-2028.  The taps are
+// accumulated tap 0 first with float32 FMA, as the reference does.  The convolution has
+// finite memory, so every (token, channel) is independent: `conv_forward` is parallel over
+// tokens and only reads the state; `conv_state_update` then writes the new state.  For a
+// step of single tokens `conv_decode` does both at once.
+#include "common.cuh"
+
+// One thread per (token, channel).
+template <typename T>
+__global__ void conv_forward_kernel(const T* __restrict__ bcx, const float* __restrict__ state,
+                                    const float* __restrict__ w, const float* __restrict__ bias,
+                                    const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                                    const int* __restrict__ seq_slot, T* __restrict__ y, int n_tokens, int D, int K,
+                                    long long state_slot_stride) {
+  const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t = blockIdx.x;
+  if (ch >= D || t >= n_tokens) return;
+  const int b = tok_seq[t];
+  const int i = t - cu_q[b];  // index of the token inside this step's part of the sequence
+  const float* st = state + (size_t)seq_slot[b] * state_slot_stride;
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int j = i - (K - 1) + k;  // source index inside this step; negative = from the state
+    float u;
+    if (j >= 0) {
+      const T* row = bcx + (size_t)(t - (i - j)) * 3 * D;
+      u = to_f32(row[ch]) * to_f32(row[2 * D + ch]);
+    } else {
+      u = st[(size_t)(K - 1 + j) * D + ch];
+    }
+    acc = fmaf(w[(size_t)k * D + ch], u, acc);
+  }
+  if (bias) acc += bias[ch];
+  y[(size_t)t * D + ch] = from_f32<T>(to_f32(bcx[(size_t)t * 3 * D + D + ch]) * acc);
+}
+
+// One thread per (sequence, channel): state <- last K-1 values of u, older state rows survive
+// when the step brought fewer than K-1 tokens (src/model.zig:2020).  Row r of the new state
+// comes from row r + Tq of the old one, which lies above r, so rows are rewritten in
+// ascending order without a copy.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ bcx, float* __restrict__ state,
+                                         const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int n_seqs,
+                                         int D, int K, long long state_slot_stride) {
+  const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  const int b = blockIdx.x;
+  if (ch >= D || b >= n_seqs) return;
+  const int t0 = cu_q[b], Tq = cu_q[b + 1] - t0;
+  if (Tq <= 0) return;
+  float* st = state + (size_t)seq_slot[b] * state_slot_stride;
+  for (int r = 0; r < K - 1; ++r) {
+    const int j = Tq - (K - 1) + r;
+    float u;
+    if (j >= 0) {
+      const T* row = bcx + (size_t)(t0 + j) * 3 * D;
+      u = to_f32(row[ch]) * to_f32(row[2 * D + ch]);
+    } else {
+      u = st[(size_t)(K - 1 + j) * D + ch];
+    }
+    st[(size_t)r * D + ch] = u;
+  }
+}
+
+// Single-token steps: one thread per (sequence, channel) reads the state, produces y and
+// shifts the state by one.  Token t belongs to sequence t.
+template <typename T>
+__global__ void conv_decode_kernel(const T* __restrict__ bcx, float* __restrict__ state, const float* __restrict__ w,
+                                   const float* __restrict__ bias, const int* __restrict__ seq_slot,
+                                   T* __restrict__ y, int n_seqs, int D, int K, long long state_slot_stride) {
+  const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  const int b = blockIdx.x;
+  if (ch >= D || b >= n_seqs) return;
+  float* st = state + (size_t)seq_slot[b] * state_slot_stride;
+  const T* row = bcx + (size_t)b * 3 * D;
+  const float u_new = to_f32(row[ch]) * to_f32(row[2 * D + ch]);
+  float acc = 0.f;
+  for (int k = 0; k < K - 1; ++k) {
+    const float u = st[(size_t)k * D + ch];
+    acc = fmaf(w[(size_t)k * D + ch], u, acc);
+    if (k > 0) st[(size_t)(k - 1) * D + ch] = u;
+  }
+  acc = fmaf(w[(size_t)(K - 1) * D + ch], u_new, acc);
+  st[(size_t)(K - 2) * D + ch] = u_new;
+  if (bias) acc += bias[ch];
+  y[(size_t)b * D + ch] = from_f32<T>(to_f32(row[D + ch]) * acc);
+}
+
+extern "C" {
+
+// bcx [n_tokens, 3D] and y [n_tokens, D] in the run dtype; state [slots, K-1, D] float32 with
+// `state_slot_stride` elements between slots; w [K, D] and bias [D] (or null) float32.
+int zk_conv_forward(const void* bcx, const float* state, const float* w, const float* bias, const int* tok_seq,
+                    const int* cu_q, const int* seq_slot, void* y, int n_tokens, int D, int K,
+                    long long state_slot_stride, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (D <= 0 || K < 2) return ZK_EINVAL;
+  const int threads = 128;
+  dim3 grid(n_tokens, ceil_div_i(D, threads));
+  if (dtype == ZK_F32)
+    conv_forward_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
+                                                             (float*)y, n_tokens, D, K, state_slot_stride);
+  else if (dtype == ZK_BF16)
+    conv_forward_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
+                                                            (bf16*)y, n_tokens, D, K, state_slot_stride);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
+
+int zk_conv_state_update(const void* bcx, float* state, const int* cu_q, const int* seq_slot, int n_seqs, int D, int K,
+                         long long state_slot_stride, int dtype, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (D <= 0 || K < 2) return ZK_EINVAL;
+  const int threads = 128;
+  dim3 grid(n_seqs, ceil_div_i(D, threads));
+  if (dtype == ZK_F32)
+    conv_state_update_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, cu_q, seq_slot, n_seqs, D,
+                                                                  K, state_slot_stride);
+  else if (dtype == ZK_BF16)
+    conv_state_update_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, cu_q, seq_slot, n_seqs, D, K,
+                                                                 state_slot_stride);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
+
+int zk_conv_decode(const void* bcx, float* state, const float* w, const float* bias, const int* seq_slot, void* y,
+                   int n_seqs, int D, int K, long long state_slot_stride, int dtype, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (D <= 0 || K < 2) return ZK_EINVAL;
+  const int threads = 128;
+  dim3 grid(n_seqs, ceil_div_i(D, threads));
+  if (dtype == ZK_F32)
+    conv_decode_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, w, bias, seq_slot, (float*)y,
+                                                            n_seqs, D, K, state_slot_stride);
+  else if (dtype == ZK_BF16)
+    conv_decode_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, seq_slot, (bf16*)y, n_seqs,
+                                                           D, K, state_slot_stride);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
+
+}  // extern "C"

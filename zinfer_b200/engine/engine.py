@@ -1,0 +1,159 @@
+"""The step function and the engine that owns a model's cache.
+
+The reference's step is `State.forwardN(tokens, n_logits)`: embed, run every layer over the
+given tokens from the cache, advance the position, and return logits of the last `n_logits`
+rows; long prompts are cut into chunks (src/model.zig:2519-2542, 2347-2516).  `Engine.step` is
+that function for a batch: for each sequence its next tokens (whole prompts in a batch's first
+step, one token each afterwards), run as one packed batch from the cache, logits returned at
+the wanted places only.  Nothing but the given tokens is computed, and padding does not exist:
+sequences of unequal length are packed, not padded.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheManager
+from ..models.model import Model
+from .context import CallContext, StepContext, batch_layout, pack_batch
+
+
+class StepError(RuntimeError):
+    """The device reported a fault of the step's inputs (a token id outside the vocabulary, a
+    position without a page)."""
+
+
+_STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's position has no cache page"}
+
+
+class Engine:
+    def __init__(self, model: Model, max_batch: int = 64, max_seq_len: Optional[int] = None,
+                 max_tokens: Optional[int] = None, page_size: int = 64, max_step_tokens: int = 8192,
+                 attn_split_keys: int = 0):
+        """max_batch: slots (sequences alive at once).  max_seq_len: longest sequence, default
+        the model's max_position_embeddings.  max_tokens: tokens the cache holds in total, each
+        sequence rounded up to whole pages; default max_batch * max_seq_len.  max_step_tokens:
+        a step with more tokens runs as several packed chunks.  attn_split_keys: keys per
+        chunk of single-token attention (0 = chosen per step)."""
+        kernels.require_cuda()
+        if model.device is None:
+            raise ValueError("the model has no weights loaded")
+        self.model = model
+        self.dtype, self.device = model.dtype, model.device
+        cfg = model.config
+        self.max_seq_len = int(max_seq_len or cfg.max_position_embeddings)
+        if max_tokens is None:
+            max_tokens = max_batch * (-(-self.max_seq_len // page_size) * page_size)
+        self.max_step_tokens = max(1, int(max_step_tokens))
+        self.attn_split_keys = int(attn_split_keys)
+        self.cache = CacheManager(model.cache_specs(), max_batch, int(max_tokens), self.max_seq_len, page_size,
+                                  self.dtype, self.device)
+        self.calls = [CallContext(c, call.layer, self.cache.kv_view(c), self.cache.writes_kv(c),
+                                  self.cache.state_view(c)) for c, call in enumerate(model.schedule)]
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.vocab_size = cfg.vocab_size
+
+    # ------------------------------------------------------------------ sequences
+    def start(self, n: int) -> list[int]:
+        """Slots for `n` new sequences that start together."""
+        return self.cache.alloc_slots(n)
+
+    def finish(self, slots: Sequence[int]) -> None:
+        """Gives the slots and all they hold back to the cache."""
+        self.cache.free_slots(slots)
+
+    def length(self, slot: int) -> int:
+        return int(self.cache.lengths[slot])
+
+    # ------------------------------------------------------------------ the step
+    def step(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None, check: bool = True) -> Optional[torch.Tensor]:
+        """Feeds `token_lists[i]` to the sequence in `slots[i]` and returns float32 logits
+        [wanted, vocab] on the device, in the order of the sequences and of `want[i]` (indices
+        into token_lists[i]; default: the last token of each sequence).  Returns None if nothing
+        is wanted.  Raises ContextFull / OutOfPages before anything is changed."""
+        if len(slots) != len(token_lists):
+            raise ValueError("one token list per slot")
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot is named twice in one step")
+        lens = [len(t) for t in token_lists]
+        if any(l == 0 for l in lens):
+            raise ValueError("every sequence of a step brings at least one token")
+        if want is None:
+            want = [[l - 1] for l in lens]
+        for w, l in zip(want, lens):
+            if any(not 0 <= i < l for i in w):
+                raise ValueError(f"wanted position outside the {l} tokens of its sequence")
+        self.cache.reserve(slots, lens)
+        self.cache.sync()
+
+        pieces = []
+        total = sum(lens)
+        if total <= self.max_step_tokens:
+            out = self._run(slots, [int(self.cache.lengths[s]) for s in slots], token_lists, want)
+            if out is not None:
+                pieces.append((None, out))
+            order = None
+        else:
+            order = self._run_chunked(slots, token_lists, want, pieces)
+        self.cache.advance(slots, lens)
+        if check:
+            self.check_status()
+        if not pieces:
+            return None
+        if order is None:
+            return pieces[0][1]
+        logits = torch.cat([p[1] for p in pieces], dim=0)
+        # chunks produce wanted rows chunk by chunk; put them into request order
+        keys = [k for p in pieces for k in p[0]]
+        perm = sorted(range(len(keys)), key=lambda i: keys[i])
+        return logits[torch.tensor(perm, device=logits.device)]
+
+    def _run_chunked(self, slots, token_lists, want, pieces):
+        """Runs a large step as packed chunks of at most max_step_tokens tokens.  Every chunk is
+        itself a step that continues each sequence where the previous chunk left it, so the cut
+        shows only as rounding."""
+        done = [0] * len(slots)
+        base = [int(self.cache.lengths[s]) for s in slots]
+        lens = [len(t) for t in token_lists]
+        while any(d < l for d, l in zip(done, lens)):
+            room = self.max_step_tokens
+            sub_idx, sub_tokens, sub_want, sub_keys = [], [], [], []
+            for i, (d, l) in enumerate(zip(done, lens)):
+                if d >= l or room == 0:
+                    continue
+                take = min(l - d, room)
+                room -= take
+                sub_idx.append(i)
+                sub_tokens.append(token_lists[i][d:d + take])
+                w = [(j, p) for j, p in enumerate(want[i]) if d <= p < d + take]
+                sub_want.append([p - d for _, p in w])
+                sub_keys.extend((i, j) for j, _ in w)
+            out = self._run([slots[i] for i in sub_idx], [base[i] + done[i] for i in sub_idx], sub_tokens, sub_want)
+            if out is not None:
+                pieces.append((sub_keys, out))
+            for i, t in zip(sub_idx, sub_tokens):
+                done[i] += len(t)
+        return True
+
+    def _run(self, slots, starts, token_lists, want) -> Optional[torch.Tensor]:
+        lens = [len(t) for t in token_lists]
+        n, B = sum(lens), len(slots)
+        host = pack_batch(slots, starts, token_lists)
+        buf = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        max_kv = max(s + l for s, l in zip(starts, lens))
+        ctx = StepContext(self.dtype, self.device, self.status, buf, n, B, lens, max_kv, self.attn_split_keys)
+        cu = np.concatenate([[0], np.cumsum(lens)])
+        rows = [int(cu[b]) + int(i) for b, w in enumerate(want) for i in w]
+        want_rows = torch.tensor(rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True) if rows else None
+        return self.model.forward(ctx, self.calls, want_rows)
+
+    def check_status(self) -> None:
+        """Synchronises and raises StepError if a kernel flagged its inputs."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise StepError(_STATUS_TEXT.get(code, f"device status {code}"))

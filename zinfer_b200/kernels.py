@@ -1,0 +1,324 @@
+"""Python face of the hand-written sm_100a kernels in `csrc/`.
+
+Every function checks its tensors (device, dtype, layout, sizes), launches one kernel on the
+current CUDA stream through the library's C entry point and raises `KernelError` if the
+launcher refuses the sizes or CUDA reports an error.  There is no other implementation behind
+these functions: without a CUDA device, a compiler or a loadable library they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import KernelBuildError, load_library
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_C = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "l": ctypes.c_longlong}
+
+# library -> function -> argument kinds (p pointer, i int, f float, l long long); the last
+# pointer of every launcher is the stream
+_SIGNATURES = {
+    "elementwise": {
+        "zk_embed": "pppiiifipp",
+        "zk_rmsnorm": "ppppiifip",
+        "zk_silu_mul": "ppiiip",
+    },
+    "gemm_simt": {
+        "zk_gemm_simt": "ppppiiiiiiiiip",
+    },
+    "shortconv": {
+        "zk_conv_forward": "ppppppppiiilip",
+        "zk_conv_state_update": "ppppiiilip",
+        "zk_conv_decode": "ppppppiiilip",
+    },
+    "attention": {
+        "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiipp",
+        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiiip",
+        "zk_attn_merge": "pppiiiip",
+        "zk_attn_rows_per_block": "",
+        "zk_attn_max_head_dim": "",
+    },
+}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or CUDA reported a failure."""
+
+
+_funcs: dict[str, object] = {}
+
+
+def _fn(lib_name: str, fn_name: str):
+    f = _funcs.get(fn_name)
+    if f is None:
+        lib = load_library(lib_name)
+        for name, sig in _SIGNATURES[lib_name].items():
+            g = getattr(lib, name)
+            g.argtypes = [_C[c] for c in sig]
+            g.restype = ctypes.c_int
+            _funcs[name] = g
+        f = _funcs[fn_name]
+    return f
+
+
+def _error_name(code: int) -> str:
+    lib = load_library("elementwise")
+    lib.zk_error_name.argtypes = [ctypes.c_int]
+    lib.zk_error_name.restype = ctypes.c_char_p
+    s = lib.zk_error_name(code)
+    return s.decode() if s else f"status {code}"
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_error_name(code)} (status {code})")
+
+
+def require_cuda() -> None:
+    """Raises unless a CUDA device is usable; the product path has no CPU implementation."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: zinfer_b200 runs on sm_100a GPUs only and has no CPU path")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None, contiguous=True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor")
+    if dtype is not None:
+        ok = t.dtype in dtype if isinstance(dtype, (tuple, list)) else t.dtype == dtype
+        if not ok:
+            raise KernelError(f"{name}: dtype {t.dtype}, expected {dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous")
+    if shape is not None:
+        if t.dim() != len(shape) or any(s is not None and s != d for s, d in zip(shape, t.shape)):
+            raise KernelError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not a run dtype (float32, bfloat16)") from None
+
+
+# ------------------------------------------------------------------------------- row kernels
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """x[t] = float32(table[tokens[t]]) * scale; bad ids set status to 1."""
+    _need(tokens, "tokens", torch.int32)
+    _need(table, "table", (torch.float32, torch.bfloat16), (None, None))
+    _need(status, "status", torch.int32)
+    n, (vocab, dim) = tokens.numel(), table.shape
+    x = torch.empty((n, dim), dtype=torch.float32, device=table.device)
+    _check(_fn("elementwise", "zk_embed")(_ptr(tokens), _ptr(table), _ptr(x), n, dim, vocab, scale,
+                                          dtype_code(table.dtype), _ptr(status), _stream()), "embed")
+    return x
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of float32 rows (all, or those listed in `rows`) into `out_dtype`."""
+    _need(x, "x", torch.float32, (None, None))
+    dim = x.shape[1]
+    _need(weight, "weight", torch.float32, (dim,))
+    n_out = x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    y = torch.empty((n_out, dim), dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "zk_rmsnorm")(_ptr(x), _ptr(rows), _ptr(weight), _ptr(y), n_out, dim, eps,
+                                            dtype_code(out_dtype), _stream()), "rmsnorm")
+    return y
+
+
+def silu_mul(gu: torch.Tensor) -> torch.Tensor:
+    """h = silu(gu[:, :F]) * gu[:, F:]."""
+    _need(gu, "gu", (torch.float32, torch.bfloat16), (None, None))
+    n, two_f = gu.shape
+    if two_f % 2:
+        raise KernelError(f"silu_mul: width {two_f} is not even")
+    h = torch.empty((n, two_f // 2), dtype=gu.dtype, device=gu.device)
+    _check(_fn("elementwise", "zk_silu_mul")(_ptr(gu), _ptr(h), n, two_f // 2, dtype_code(gu.dtype), _stream()),
+           "silu_mul")
+    return h
+
+
+# ------------------------------------------------------------------------------- contractions
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+              accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias) with float32 FMA on the CUDA cores.  a [M, K], w [N, K] share a
+    dtype; out is that dtype or float32; accumulate needs a float32 or same-dtype `out`."""
+    _need(a, "a", (torch.float32, torch.bfloat16), (None, None))
+    _need(w, "w", a.dtype, (None, a.shape[1]))
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    _need(out, "out", (torch.float32, a.dtype), (M, N))
+    if a.dtype == torch.float32 and out.dtype != torch.float32:
+        raise KernelError("gemm: float32 inputs need a float32 output")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (N,))
+    _check(_fn("gemm_simt", "zk_gemm_simt")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0), w.stride(0),
+                                            out.stride(0), dtype_code(a.dtype), dtype_code(out.dtype),
+                                            1 if accumulate else 0, _stream()), "gemm_simt")
+    return out
+
+
+# ------------------------------------------------------------------------------- short convolution
+
+def conv_forward(bcx, state, w, bias, tok_seq, cu_q, seq_slot) -> torch.Tensor:
+    """y of the gated short convolution for a packed batch; reads `state`, does not change it.
+    bcx [n, 3D]; state [slots, K-1, D] float32; w [K, D] float32; bias [D] float32 or None."""
+    _need(bcx, "bcx", (torch.float32, torch.bfloat16), (None, None))
+    n, three_d = bcx.shape
+    D = three_d // 3
+    _need(w, "conv weight", torch.float32, (None, D))
+    K = w.shape[0]
+    _need(state, "conv state", torch.float32, (None, K - 1, D))
+    if bias is not None:
+        _need(bias, "conv bias", torch.float32, (D,))
+    for t, nm in ((tok_seq, "tok_seq"), (cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    y = torch.empty((n, D), dtype=bcx.dtype, device=bcx.device)
+    _check(_fn("shortconv", "zk_conv_forward")(_ptr(bcx), _ptr(state), _ptr(w), _ptr(bias), _ptr(tok_seq), _ptr(cu_q),
+                                               _ptr(seq_slot), _ptr(y), n, D, K, state.stride(0),
+                                               dtype_code(bcx.dtype), _stream()), "conv_forward")
+    return y
+
+
+def conv_state_update(bcx, state, cu_q, seq_slot, n_seqs: int, K: int) -> None:
+    """state[slot] <- the last K-1 values of B*X of each sequence (older rows kept if fewer came)."""
+    _need(bcx, "bcx", (torch.float32, torch.bfloat16), (None, None))
+    D = bcx.shape[1] // 3
+    _need(state, "conv state", torch.float32, (None, K - 1, D))
+    _check(_fn("shortconv", "zk_conv_state_update")(_ptr(bcx), _ptr(state), _ptr(cu_q), _ptr(seq_slot), n_seqs, D, K,
+                                                    state.stride(0), dtype_code(bcx.dtype), _stream()),
+           "conv_state_update")
+
+
+def conv_decode(bcx, state, w, bias, seq_slot) -> torch.Tensor:
+    """Single-token step: y and the shifted state in one kernel; row b of bcx is sequence b."""
+    _need(bcx, "bcx", (torch.float32, torch.bfloat16), (None, None))
+    n, three_d = bcx.shape
+    D = three_d // 3
+    _need(w, "conv weight", torch.float32, (None, D))
+    K = w.shape[0]
+    _need(state, "conv state", torch.float32, (None, K - 1, D))
+    if bias is not None:
+        _need(bias, "conv bias", torch.float32, (D,))
+    _need(seq_slot, "seq_slot", torch.int32)
+    y = torch.empty((n, D), dtype=bcx.dtype, device=bcx.device)
+    _check(_fn("shortconv", "zk_conv_decode")(_ptr(bcx), _ptr(state), _ptr(w), _ptr(bias), _ptr(seq_slot), _ptr(y), n,
+                                              D, K, state.stride(0), dtype_code(bcx.dtype), _stream()), "conv_decode")
+    return y
+
+
+# ------------------------------------------------------------------------------- attention
+
+def attn_rows_per_block() -> int:
+    return _fn("attention", "zk_attn_rows_per_block")()
+
+
+def attn_max_head_dim() -> int:
+    return _fn("attention", "zk_attn_max_head_dim")()
+
+
+def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, n_heads: int,
+               n_kv: int, head_dim: int, n_rot: int, interleaved: bool, eps: float, status, write_kv: bool = True):
+    """Per-head RMSNorm of q and k (if weights are given), rotary encoding (if `inv_freq` is
+    given), q out as [n, H*hd], and k, v written to their pages.  k_cache / v_cache are one
+    layer's [pages, Hkv, page_size, hd]."""
+    _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, (n_heads + 2 * n_kv) * head_dim))
+    n = qkv.shape[0]
+    for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+        _need(c, nm, qkv.dtype, (None, n_kv, None, head_dim))
+    page_size = k_cache.shape[2]
+    if head_dim % 2 or head_dim > attn_max_head_dim():
+        raise KernelError(f"qk_prepare: head_dim {head_dim} must be even and <= {attn_max_head_dim()}")
+    for wt, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
+        if wt is not None:
+            _need(wt, nm, torch.float32, (head_dim,))
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, (n_rot // 2,))
+    _need(page_table, "page_table", torch.int32, (None, None))
+    q = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    _check(_fn("attention", "zk_qk_prepare")(
+        _ptr(qkv), _ptr(q), None, _ptr(k_cache), _ptr(v_cache), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _ptr(tok_seq),
+        _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, n_rot,
+        1 if interleaved else 0, eps, page_size, 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), _stream()),
+        "qk_prepare")
+    return q
+
+
+def qk_normed(qkv, q_w, k_w, n_heads: int, n_kv: int, head_dim: int, eps: float, tok_pos, status) -> torch.Tensor:
+    """Per-head RMSNorm of the q and k heads of qkv [n, (H + 2 Hkv) * hd] into a new tensor of
+    the same shape (v copied); no rotation, no cache write."""
+    _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, (n_heads + 2 * n_kv) * head_dim))
+    if head_dim % 2 or head_dim > attn_max_head_dim():
+        raise KernelError(f"qk_normed: head_dim {head_dim} must be even and <= {attn_max_head_dim()}")
+    for wt, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
+        if wt is not None:
+            _need(wt, nm, torch.float32, (head_dim,))
+    dense = torch.empty_like(qkv)
+    _check(_fn("attention", "zk_qk_prepare")(
+        _ptr(qkv), None, _ptr(dense), None, None, _ptr(q_w), _ptr(k_w), None, None, _ptr(tok_pos), None, None, 0,
+        qkv.shape[0], n_heads, n_kv, head_dim, 0, 0, eps, 1, 0, dtype_code(qkv.dtype), _ptr(status), _stream()),
+        "qk_normed")
+    return dense
+
+
+def attn_tile_shape(n_heads: int, n_kv: int) -> tuple[int, int]:
+    """(tokens per query tile, heads of a KV group per block) for these head counts."""
+    rows = attn_rows_per_block()
+    gc = min(n_heads // n_kv, rows)
+    return max(1, rows // gc), gc
+
+
+def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, n_heads: int, n_kv: int,
+              head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0) -> torch.Tensor:
+    """Causal grouped-query attention of a packed batch against the paged cache.  With
+    num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards."""
+    _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
+    n = q.shape[0]
+    for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+        _need(c, nm, q.dtype, (None, n_kv, None, head_dim))
+    page_size = k_cache.shape[2]
+    if n_heads % n_kv:
+        raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv} KV heads")
+    if head_dim > attn_max_head_dim():
+        raise KernelError(f"attention: head_dim {head_dim} exceeds {attn_max_head_dim()}")
+    bq, gc = attn_tile_shape(n_heads, n_kv)
+    n_tiles = tile_seq.numel()
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = torch.empty((num_splits, n * n_heads, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
+    _check(_fn("attention", "zk_attn_fwd")(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
+        _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,
+        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), _stream()),
+        "attention")
+    if num_splits > 1:
+        _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
+                                                 num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+    return out
+
+
+__all__ = [n for n in dir() if not n.startswith("_")] + ["KernelBuildError"]

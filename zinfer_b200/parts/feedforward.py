@@ -1,0 +1,35 @@
+"""SwiGLU feed-forward: h = silu(xn W1^T) * (xn W3^T), out (+)= h W2^T
+(src/model.zig:2411-2422, 1085-1117; silu(g) = g / (1 + exp(-g)), src/ffn.zig:31-33).
+W1 and W3 are stacked at load into one [2F, D] matrix so that gate and up are one contraction,
+as the reference computes both in one worker."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import FEED_FORWARDS, FeedForward, WeightSpec
+from .linear import linear
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden: int, ffn_dim: int, gate_name: str, up_name: str, down_name: str):
+        self.hidden, self.ffn_dim = hidden, ffn_dim
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.gate_name, (self.ffn_dim, self.hidden)),
+                WeightSpec(self.up_name, (self.ffn_dim, self.hidden)),
+                WeightSpec(self.down_name, (self.hidden, self.ffn_dim))]
+
+    def load(self, weights, dtype, device):
+        self.w_gate_up = torch.cat([weights[self.gate_name], weights[self.up_name]], dim=0).contiguous()
+        self.w_down = weights[self.down_name]
+
+    def forward(self, ctx, xn, out, accumulate):
+        gu = linear(xn, self.w_gate_up)
+        h = kernels.silu_mul(gu)
+        linear(h, self.w_down, out=out, accumulate=accumulate)
+
+
+FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -1,0 +1,67 @@
+"""Gated short-convolution mixer (src/model.zig:1994-2028).
+
+[B, C, X] = xn W_in^T in that order along the 3D outputs; u = B * X; a causal depthwise
+convolution of K taps over u, whose inputs before the step come from the sequence's state (the
+last K-1 values of u, zero at a sequence's start); y = C * conv; out (+)= y W_out^T; the state
+becomes the last K-1 values of u.  The taps are stored [K, D] (tap, channel), transposed from
+the file's [D, 1, K] at load as the reference does (src/model.zig:788-802).
+
+The reference has no bias tensors for this mixer (src/model.zig:729-734).  With `conv_bias` a
+bias [D] is added to the convolution before the C gate, and biases of the two projections are
+used when the file carries them.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import MIXERS, Mixer, StateRequest, WeightSpec
+from .linear import linear
+
+
+class ShortConv(Mixer):
+    def __init__(self, hidden: int, kernel_size: int, in_name: str, conv_name: str, out_name: str,
+                 conv_bias_name: str | None = None, in_bias_name: str | None = None,
+                 out_bias_name: str | None = None):
+        if kernel_size < 2:
+            raise ValueError(f"a short convolution needs >= 2 taps, got {kernel_size}")       # src/model.zig:486
+        self.hidden, self.K = hidden, kernel_size
+        self.in_name, self.conv_name, self.out_name = in_name, conv_name, out_name
+        self.conv_bias_name, self.in_bias_name, self.out_bias_name = conv_bias_name, in_bias_name, out_bias_name
+        self.w_in = self.w_out = self.taps = self.conv_bias = self.in_bias = self.out_bias = None
+
+    def weight_specs(self):
+        D, K = self.hidden, self.K
+        specs = [WeightSpec(self.in_name, (3 * D, D)),
+                 WeightSpec(self.conv_name, (D, K), role="vector", alt_shapes=((D, 1, K),)),
+                 WeightSpec(self.out_name, (D, D))]
+        if self.conv_bias_name:
+            specs.append(WeightSpec(self.conv_bias_name, (D,), role="vector"))
+        if self.in_bias_name:
+            specs.append(WeightSpec(self.in_bias_name, (3 * D,), role="vector", optional=True, init="skip"))
+        if self.out_bias_name:
+            specs.append(WeightSpec(self.out_bias_name, (D,), role="vector", optional=True, init="skip"))
+        return specs
+
+    def load(self, weights, dtype, device):
+        self.w_in, self.w_out = weights[self.in_name], weights[self.out_name]
+        self.taps = weights[self.conv_name].reshape(self.hidden, self.K).t().contiguous()
+        self.conv_bias = weights.get(self.conv_bias_name) if self.conv_bias_name else None
+        self.in_bias = weights.get(self.in_bias_name) if self.in_bias_name else None
+        self.out_bias = weights.get(self.out_bias_name) if self.out_bias_name else None
+
+    def state_request(self):
+        return StateRequest((self.K - 1, self.hidden), torch.float32)
+
+    def forward(self, ctx, call, xn, out, accumulate):
+        bcx = linear(xn, self.w_in, bias=self.in_bias)
+        state = call.state
+        if ctx.is_decode:
+            y = kernels.conv_decode(bcx, state, self.taps, self.conv_bias, ctx.seq_slot)
+        else:
+            y = kernels.conv_forward(bcx, state, self.taps, self.conv_bias, ctx.tok_seq, ctx.cu_q, ctx.seq_slot)
+            kernels.conv_state_update(bcx, state, ctx.cu_q, ctx.seq_slot, ctx.n_seqs, self.K)
+        linear(y, self.w_out, out=out, accumulate=accumulate, bias=self.out_bias)
+
+
+MIXERS.register("short_conv", ShortConv)
