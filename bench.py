@@ -1,0 +1,261 @@
+"""Benchmark of zinfer_b200: decode tokens per second of an LFM2-1.2B-shaped model with random
+weights on one B200, with the prefill rate, the decode roofline and batch-1/64 points beside it.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one decode step: one new token for each of the batch's sequences.  After W warm-up
+steps exactly K steps are timed with CUDA events on the launching stream.  The step reads 2.3 GB
+of weights and the live requests' cache, far more than the 126 MB L2, so no flush is needed
+between iterations.  The line printed is one JSON object; `value` is device-timed, `e2e` is the
+same metric through `Engine.generate` with token ids going in from and coming back to the host
+every step.  The reference engine (a Zig program for CPUs) cannot be installed as a Python
+package, so `--impl reference` prints an `unavailable` line.  This library runs on one GPU: for
+--gpus > 1 the program says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+
+# LFM2-1.2B: the sizes of the published checkpoint's config.json
+LFM2_1_2B = dict(
+    architectures=["Lfm2ForCausalLM"], model_type="lfm2", vocab_size=65536, hidden_size=2048, num_hidden_layers=16,
+    num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=128000,
+    layer_types=["conv", "conv", "full_attention", "conv", "conv", "full_attention", "conv", "conv", "full_attention",
+                 "conv", "full_attention", "conv", "full_attention", "conv", "full_attention", "conv"],
+    block_ff_dim=12288, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=256,
+    conv_L_cache=3, conv_bias=False, rope_theta=1000000.0, norm_eps=1e-5, tie_word_embeddings=True, eos_token_id=7)
+CONTEXT = 4096
+PROMPT_RANGE = (512, 2048)
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+        except (KeyError, ValueError, json.JSONDecodeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines: list[str] = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            sm.append(int(f[0]))
+            mx = max(mx, int(f[1]) if f[1].isdigit() else 0)
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, n_layers_run: int) -> dict:
+    """Weight bytes a decode step reads and FLOPs a prefill needs, from the configuration."""
+    D, F, Q, KV, V = cfg.hidden_size, cfg.ffn_dim, cfg.q_dim, cfg.kv_dim, cfg.vocab_size
+    kinds = cfg.layer_types[:n_layers_run]
+    conv = 3 * D * D + D * D
+    attn = (Q + 2 * KV) * D + D * Q
+    ffn = 3 * D * F
+    layer_params = sum((conv if k == "conv" else attn) + ffn for k in kinds)
+    n_attn = sum(k != "conv" for k in kinds)
+    return {"layer_params": layer_params, "head_params": V * D, "n_attn": n_attn, "n_conv": len(kinds) - n_attn,
+            "kv_bytes_per_token": n_attn * 2 * KV * 2, "conv_state_bytes": (len(kinds) - n_attn) * (cfg.conv_L_cache - 1) * D * 4}
+
+
+def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int):
+    """Prefills `batch` prompts of lengths uniform in PROMPT_RANGE, then times `steps` decode steps.
+    Returns (ms per step, total cached tokens at the middle of the timed region, launches per step)."""
+    from zinfer_b200 import kernels
+    lens = rng.integers(PROMPT_RANGE[0], PROMPT_RANGE[1] + 1, size=batch).tolist()
+    prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
+    slots = engine.start(batch)
+    try:
+        engine.step(slots, prompts, want=[[] for _ in prompts])
+        toks = rng.integers(0, vocab, size=(warmup + steps, batch))
+        launches = None
+        for i in range(warmup):
+            before = kernels.launch_count
+            engine.decode(slots, toks[i].tolist())
+            if launches is None:
+                launches = kernels.launch_count - before
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(warmup, warmup + steps):
+            engine.decode(slots, toks[i].tolist())
+        stop.record()
+        torch.cuda.synchronize()
+        engine.check_status()
+        ms = start.elapsed_time(stop) / steps
+        cached = sum(lens) + batch * (warmup + steps // 2)
+    finally:
+        engine.finish(slots)
+    return ms, cached, launches
+
+
+def own_arm(args) -> dict:
+    import numpy as np
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    import zinfer_b200 as z
+    from zinfer_b200 import kernels
+
+    kernels.require_cuda()
+    pk = peaks()
+    cfg_dict = dict(LFM2_1_2B)
+    layers_cfg = cfg_dict["num_hidden_layers"]
+    if args.layers and args.layers < layers_cfg:
+        cfg_dict["num_hidden_layers"] = args.layers
+        cfg_dict["layer_types"] = cfg_dict["layer_types"][:args.layers]
+    cfg = z.config_from_dict(cfg_dict)
+    model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True)
+    B = args.batch
+    engine = z.Engine(model, max_batch=64, max_seq_len=CONTEXT, max_tokens=64 * CONTEXT, page_size=64)
+    rng = np.random.default_rng(0)
+    num = model_numbers(cfg, cfg.num_hidden_layers)
+    weight_bytes = 2 * (num["layer_params"] + num["head_params"])
+
+    # decode at the headline batch, device-timed, with the clocks sampled meanwhile
+    with ClockSampler() as clocks:
+        ms, cached, launches = time_decode(engine, torch, rng, B, args.steps, args.warmup, cfg.vocab_size)
+    value = B / (ms * 1e-3)
+    step_bytes = weight_bytes + cached * num["kv_bytes_per_token"] + B * num["conv_state_bytes"] * 2
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    # other batch sizes
+    points = {}
+    for b in (1, 64):
+        pms, _, _ = time_decode(engine, torch, rng, b, max(8, args.steps // 2), args.warmup, cfg.vocab_size)
+        points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+
+    # prefill of 2,048 tokens, one sequence
+    toks = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
+    times = []
+    for i in range(args.warmup + 5):
+        slot = engine.start(1)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step(slot, [toks], check=False)
+        stop.record()
+        torch.cuda.synchronize()
+        engine.finish(slot)
+        if i >= args.warmup:
+            times.append(start.elapsed_time(stop))
+    pre_ms = statistics.median(times)
+    T = PREFILL_TOKENS
+    flops = 2 * T * num["layer_params"] + 2 * num["head_params"] + num["n_attn"] * 2 * T * T * cfg.q_dim
+    prefill = {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # the same metric end to end through the public entry point: host token ids in and out every step
+    prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).tolist()
+               for n in rng.integers(PROMPT_RANGE[0], PROMPT_RANGE[1] + 1, size=B)]
+    engine.generate(prompts, max_new_tokens=args.warmup + 2, temp=0.0, stop_ids=[])
+    n_new = args.steps + 1
+    engine.generate(prompts, max_new_tokens=n_new, temp=0.0, stop_ids=[])
+    st = engine.stats
+    e2e_value = B * st.n_decode_steps / st.t_gen_s
+    from zinfer_b200.engine.context import batch_layout
+    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch_layout(B, B)["_total"][0],
+           "d2h_bytes_per_step": 4 * (B + 1)}
+
+    return {
+        "metric": "decode tokens/s at batch 8 (LFM2-1.2B shape, random weights, context 4096)" if B == 8
+        else f"decode tokens/s at batch {B} (LFM2-1.2B shape, random weights, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random-init weights N(0, 0.02)", "impl": "zinfer_b200",
+        "config": {"model": "LFM2-1.2B", "global_batch": B, "seq_len": CONTEXT, "parallelism": "none",
+                   "vocab": cfg.vocab_size, "hidden": cfg.hidden_size, "layers": cfg.num_hidden_layers,
+                   "layers_of_config": layers_cfg, "attn_layers": num["n_attn"], "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "ffn": cfg.ffn_dim,
+                   "conv_window": cfg.conv_L_cache, "prompt_lens": "uniform[512,2048]", "prefill_tokens": T,
+                   "l2": "inputs larger than L2 (2.3 GB of weights per step)", "peaks": pk["source"]},
+        "clocks": clocks.summary(),
+        "e2e": e2e,
+        "gpu_launches": int(launches or 0) * args.steps,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="run only the first L layers (named in `config`)")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "pylypenko99/zinfer is a Zig program for CPUs: pip cannot install it "
+                                         "(no setup.py or pyproject.toml) and no Zig compiler is on this image"}))
+        return 0
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: zinfer_b200 runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    print(json.dumps(own_arm(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

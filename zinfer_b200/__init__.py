@@ -12,6 +12,8 @@ import torch
 from . import models as _models  # noqa: F401  (registers the architectures)
 from .config import ConfigError, Lfm2Config, config_from_dict, config_from_folder
 from .engine.engine import Engine, StepError
+from .engine.generate import GenerationResult, Stats
+from .sampling import SamplingParams
 from .weights import WeightError, load_model, random_model, write_random_model
 
 _DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp32": torch.float32, "float32": torch.float32}

@@ -108,6 +108,9 @@ def compile_library(name: str, verbose: bool = True) -> Path:
         tmp.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed on {src.name} (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
+    for old in out.parent.glob(f"{name}-*.so"):          # libraries of earlier versions of the source
+        if old != out and ".tmp" not in old.name:
+            old.unlink(missing_ok=True)
     if verbose:
         print(f"[zinfer_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out

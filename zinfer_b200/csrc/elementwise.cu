@@ -48,7 +48,40 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int
   }
 }
 
+// out[i] = mean + std * n_i with n_i standard normal, a function of (seed, i) only: two hashed
+// uniforms through Box-Muller.  Fills large random models on the device in milliseconds.
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, size_t n, unsigned long long seed, float mean, float std) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const unsigned long long h = splitmix64(seed ^ splitmix64(i));
+    const float u1 = ((float)(unsigned)(h >> 40) + 1.0f) * (1.0f / 16777216.0f);   // (0, 1]
+    const float u2 = (float)(unsigned)((h >> 8) & 0xFFFFFF) * (1.0f / 16777216.0f);  // [0, 1)
+    out[i] = from_f32<T>(mean + std * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2));
+  }
+}
+
 extern "C" {
+
+int zk_fill_normal(void* out, long long n, long long seed, float mean, float std, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+  if (dtype == ZK_F32)
+    fill_normal_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (size_t)n, (unsigned long long)seed, mean, std);
+  else if (dtype == ZK_BF16)
+    fill_normal_kernel<bf16><<<blocks, threads, 0, stream>>>((bf16*)out, (size_t)n, (unsigned long long)seed, mean, std);
+  else
+    return ZK_EINVAL;
+  return ZK_LAUNCH_STATUS();
+}
 
 // Name of a status returned by any zk_* launcher (a cudaError_t value, or ZK_EINVAL).
 const char* zk_error_name(int code) {

@@ -74,7 +74,8 @@ class StepContext:
     """One step's batch on the device.  Built by the engine; parts only read it."""
 
     def __init__(self, dtype: torch.dtype, device, status: torch.Tensor, buf: torch.Tensor, n_tokens: int,
-                 n_seqs: int, q_lens: Sequence[int], max_kv_len: int, split_keys: int = 0):
+                 n_seqs: int, q_lens: Sequence[int], max_kv_len: int, split_keys: int = 0,
+                 tiles: Optional[dict] = None):
         self.dtype, self.device, self.status = dtype, device, status
         self.n_tokens, self.n_seqs = n_tokens, n_seqs
         self.q_lens = list(q_lens)
@@ -87,7 +88,8 @@ class StepContext:
         for name in ("tokens", "tok_seq", "tok_pos", "cu_q", "seq_start", "seq_slot"):
             o, size = lay[name]
             setattr(self, name, buf[o:o + size])
-        self._tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+        # query-tile tables by tile size; a caller that reuses the same batch shape may share them
+        self._tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = {} if tiles is None else tiles
 
     def attn_tiles(self, bq: int):
         """(tile_seq, tile_q0) device arrays for query tiles of `bq` tokens."""

@@ -29,15 +29,27 @@ class StepError(RuntimeError):
 _STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's position has no cache page"}
 
 
+class _DecodeGraph:
+    """A captured single-token step for one batch size: static input buffer, static output."""
+
+    def __init__(self, meta_host, meta_dev, want_rows):
+        self.meta_host, self.meta_dev, self.want_rows = meta_host, meta_dev, want_rows
+        self.tiles: dict = {}
+        self.warmed = False
+        self.graph = None
+        self.logits = None
+
+
 class Engine:
     def __init__(self, model: Model, max_batch: int = 64, max_seq_len: Optional[int] = None,
                  max_tokens: Optional[int] = None, page_size: int = 64, max_step_tokens: int = 8192,
-                 attn_split_keys: int = 0):
+                 attn_split_keys: int = 0, use_graphs: bool = True):
         """max_batch: slots (sequences alive at once).  max_seq_len: longest sequence, default
         the model's max_position_embeddings.  max_tokens: tokens the cache holds in total, each
         sequence rounded up to whole pages; default max_batch * max_seq_len.  max_step_tokens:
         a step with more tokens runs as several packed chunks.  attn_split_keys: keys per
-        chunk of single-token attention (0 = chosen per step)."""
+        chunk of single-token attention (0 = chosen per step).  use_graphs: replay single-token
+        steps of `decode` from CUDA graphs."""
         kernels.require_cuda()
         if model.device is None:
             raise ValueError("the model has no weights loaded")
@@ -55,6 +67,10 @@ class Engine:
                                   self.cache.state_view(c)) for c, call in enumerate(model.schedule)]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.vocab_size = cfg.vocab_size
+        self.use_graphs = bool(use_graphs)
+        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
+        self.stats = None
 
     # ------------------------------------------------------------------ sequences
     def start(self, n: int) -> list[int]:
@@ -150,6 +166,89 @@ class Engine:
         rows = [int(cu[b]) + int(i) for b, w in enumerate(want) for i in w]
         want_rows = torch.tensor(rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True) if rows else None
         return self.model.forward(ctx, self.calls, want_rows)
+
+    # ------------------------------------------------------------------ single-token steps
+    def decode(self, slots: Sequence[int], tokens: Sequence[int], check: bool = False) -> torch.Tensor:
+        """One token for each sequence, logits [len(slots), vocab] for all of them.  The same
+        computation as `step(slots, [[t] for t in tokens])`, replayed from a CUDA graph: a step of
+        single tokens is some 150 small kernels, and launching them one by one costs more than
+        running them.  One graph per (batch size, key-chunk layout); its first use runs
+        eagerly (which also loads every kernel), its second use is captured.  The returned
+        tensor is the graph's output buffer: use it before the next call."""
+        if not self.use_graphs:
+            return self.step(slots, [[int(t)] for t in tokens], check=check)
+        B = len(slots)
+        if B != len(tokens) or len(set(slots)) != B:
+            raise ValueError("one token per distinct slot")
+        ones = [1] * B
+        self.cache.reserve(slots, ones)
+        self.cache.sync()
+        starts = [int(self.cache.lengths[s]) for s in slots]
+        max_kv = -(-(max(starts) + 1) // 512) * 512            # bucketed, so that the key changes rarely
+        key = (B, max_kv)
+        entry = self._graphs.get(key)
+        if entry is None:
+            lay = batch_layout(B, B)["_total"][0]
+            entry = _DecodeGraph(torch.zeros(lay, dtype=torch.int32).pin_memory(),
+                                 torch.zeros(lay, dtype=torch.int32, device=self.device),
+                                 torch.arange(B, dtype=torch.int32, device=self.device))
+            self._graphs[key] = entry
+        entry.meta_host.numpy()[:] = pack_batch(slots, starts, [[int(t)] for t in tokens])
+        entry.meta_dev.copy_(entry.meta_host, non_blocking=True)
+        ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max_kv,
+                          self.attn_split_keys, tiles=entry.tiles)
+        if entry.graph is None and not entry.warmed:
+            logits = self.model.forward(ctx, self.calls, entry.want_rows)
+            entry.warmed = True
+        else:
+            if entry.graph is None:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=self._graph_pool):
+                    entry.logits = self.model.forward(ctx, self.calls, entry.want_rows)
+                entry.graph = g
+            entry.graph.replay()
+            logits = entry.logits
+        self.cache.advance(slots, ones)
+        if check:
+            self.check_status()
+        return logits
+
+    # ------------------------------------------------------------------ generation
+    def prefill(self, slots, prompts) -> torch.Tensor:
+        return self.step(slots, prompts, check=False)
+
+    def read_tokens(self, tokens: torch.Tensor) -> list[int]:
+        """Sampled tokens on the host; this is the step's synchronisation point, so the device's
+        status word is read with them."""
+        both = torch.cat([tokens.to(torch.int32), self.status]).cpu().tolist()
+        if both[-1]:
+            self.status.zero_()
+            raise StepError(_STATUS_TEXT.get(both[-1], f"device status {both[-1]}"))
+        return both[:-1]
+
+    def generate(self, prompts, max_new_tokens: int = 256, sampling=None, stop_ids=None, on_step=None,
+                 **sampling_options):
+        """Generates for every prompt (a list of token ids each); returns a GenerationResult per
+        prompt, in order.  `sampling` is a SamplingParams, or give its fields as keyword
+        arguments (temp, top_k, top_p, min_p, repeat_penalty, seed, ...; `temperature` is
+        accepted for `temp`).  stop_ids default to the configuration's eos token ids."""
+        from ..sampling.sampler import Sampler, SamplingParams
+        from .generate import GenerationLoop
+
+        if sampling is None:
+            if "temperature" in sampling_options:
+                sampling_options["temp"] = sampling_options.pop("temperature")
+            sampling = SamplingParams(**sampling_options)
+        elif sampling_options:
+            raise ValueError("give either `sampling` or its fields, not both")
+        if stop_ids is None:
+            stop_ids = self.model.config.eos_token_ids
+        sampler = Sampler(sampling, self.vocab_size, len(prompts), self.device)
+        loop = GenerationLoop(self, self.cache.max_slots, self.cache.num_pages * self.cache.page_size,
+                              self.max_seq_len, self.cache.page_size)
+        results = loop.run(prompts, sampler, max_new_tokens, stop_ids, on_step)
+        self.stats = loop.stats
+        return results
 
     def check_status(self) -> None:
         """Synchronises and raises StepError if a kernel flagged its inputs."""

@@ -26,6 +26,7 @@ _SIGNATURES = {
         "zk_embed": "pppiiifipp",
         "zk_rmsnorm": "ppppiifip",
         "zk_silu_mul": "ppiiip",
+        "zk_fill_normal": "pllffip",
     },
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
@@ -34,6 +35,11 @@ _SIGNATURES = {
         "zk_conv_forward": "ppppppppiiilip",
         "zk_conv_state_update": "ppppiiilip",
         "zk_conv_decode": "ppppppiiilip",
+    },
+    "sampling": {
+        "zk_apply_penalties": "piipifppip",
+        "zk_argmax": "piipp",
+        "zk_sample": "piififfffippp",
     },
     "attention": {
         "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiipp",
@@ -73,9 +79,15 @@ def _error_name(code: int) -> str:
     return s.decode() if s else f"status {code}"
 
 
+# Number of kernel launches made through this module since import (the benchmark reports it).
+launch_count = 0
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
     if code != 0:
         raise KernelError(f"{what}: {_error_name(code)} (status {code})")
+    launch_count += 1
 
 
 def require_cuda() -> None:
@@ -153,6 +165,14 @@ def silu_mul(gu: torch.Tensor) -> torch.Tensor:
     _check(_fn("elementwise", "zk_silu_mul")(_ptr(gu), _ptr(h), n, two_f // 2, dtype_code(gu.dtype), _stream()),
            "silu_mul")
     return h
+
+
+def fill_normal(out: torch.Tensor, seed: int, mean: float = 0.0, std: float = 1.0) -> torch.Tensor:
+    """Fills `out` with mean + std * N(0, 1), a function of (seed, element index) only."""
+    _need(out, "out", (torch.float32, torch.bfloat16))
+    _check(_fn("elementwise", "zk_fill_normal")(_ptr(out), out.numel(), seed & 0x7FFFFFFFFFFFFFFF, mean, std,
+                                                dtype_code(out.dtype), _stream()), "fill_normal")
+    return out
 
 
 # ------------------------------------------------------------------------------- contractions
@@ -318,6 +338,48 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if num_splits > 1:
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
                                                  num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+    return out
+
+
+# ------------------------------------------------------------------------------- sampling
+
+def apply_penalties(logits, rep_tokens, rep_penalty: float, dry_tokens, dry_pen) -> None:
+    """In place: repetition penalty on the listed tokens of each row ([n, R] int32, -1 = none),
+    then logits[row, tok] -= pen for the DRY pairs ([n, P] int32 / float32)."""
+    _need(logits, "logits", torch.float32, (None, None))
+    n, V = logits.shape
+    R = P = 0
+    if rep_tokens is not None:
+        _need(rep_tokens, "rep_tokens", torch.int32, (n, None))
+        R = rep_tokens.shape[1]
+    if dry_tokens is not None:
+        _need(dry_tokens, "dry_tokens", torch.int32, (n, None))
+        P = dry_tokens.shape[1]
+        _need(dry_pen, "dry_pen", torch.float32, (n, P))
+    _check(_fn("sampling", "zk_apply_penalties")(_ptr(logits), n, V, _ptr(rep_tokens), R, rep_penalty,
+                                                 _ptr(dry_tokens), _ptr(dry_pen), P, _stream()), "apply_penalties")
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Lowest index among the largest logits of each row; int32 [n]."""
+    _need(logits, "logits", torch.float32, (None, None))
+    n, V = logits.shape
+    out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "zk_argmax")(_ptr(logits), n, V, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits, uniforms, temp: float, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
+           xtc_probability: float = 0.0, xtc_threshold: float = 0.1, xtc_min_keep: int = 1) -> torch.Tensor:
+    """One draw per row after top-k, top-p, min-p, temperature and XTC; uniforms [n, 2] in [0, 1)."""
+    _need(logits, "logits", torch.float32, (None, None))
+    n, V = logits.shape
+    _need(uniforms, "uniforms", torch.float32, (n, 2))
+    if not temp > 0:
+        raise KernelError("sample: temperature must be positive (use argmax for greedy)")
+    out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "zk_sample")(_ptr(logits), n, V, temp, top_k, top_p, min_p, xtc_probability, xtc_threshold,
+                                        xtc_min_keep, _ptr(uniforms), _ptr(out), _stream()), "sample")
     return out
 
 

@@ -1,0 +1,1 @@
+from .sampler import Sampler, SamplingParams, dry_penalties, recent_distinct, uniform
