@@ -145,6 +145,28 @@ def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: 
     return ms, cached, launches
 
 
+def time_prefill(engine, torch, rng, cfg, warmup: int, num: dict, pk: dict) -> dict:
+    """One sequence of PREFILL_TOKENS tokens in one step; median of 5 after the warm-up."""
+    toks = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
+    times = []
+    for i in range(warmup + 5):
+        slot = engine.start(1)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step(slot, [toks], check=False)
+        stop.record()
+        torch.cuda.synchronize()
+        engine.finish(slot)
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    pre_ms = statistics.median(times)
+    T = PREFILL_TOKENS
+    flops = 2 * T * num["layer_params"] + 2 * num["head_params"] + num["n_attn"] * 2 * T * T * cfg.q_dim
+    return {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
+            "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+
 def own_arm(args) -> dict:
     import numpy as np
     import torch
@@ -163,7 +185,11 @@ def own_arm(args) -> dict:
     cfg = z.config_from_dict(cfg_dict)
     model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True)
     B = args.batch
-    engine = z.Engine(model, max_batch=64, max_seq_len=CONTEXT, max_tokens=64 * CONTEXT, page_size=64)
+    engine = z.Engine(model, max_batch=64, max_seq_len=CONTEXT, max_tokens=64 * CONTEXT, page_size=64,
+                      use_graphs=not args.no_graphs)
+    if args.only == "prefill":
+        return {"prefill": time_prefill(engine, torch, np.random.default_rng(0), cfg, args.warmup,
+                                        model_numbers(cfg, cfg.num_hidden_layers), pk)}
     rng = np.random.default_rng(0)
     num = model_numbers(cfg, cfg.num_hidden_layers)
     weight_bytes = 2 * (num["layer_params"] + num["head_params"])
@@ -175,31 +201,18 @@ def own_arm(args) -> dict:
     step_bytes = weight_bytes + cached * num["kv_bytes_per_token"] + B * num["conv_state_bytes"] * 2
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
+    if args.only == "decode":
+        return {"value": round(value, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches,
+                "roofline_frac": round(achieved / pk["hbm_gbs"], 4)}
+
     # other batch sizes
     points = {}
     for b in (1, 64):
         pms, _, _ = time_decode(engine, torch, rng, b, max(8, args.steps // 2), args.warmup, cfg.vocab_size)
         points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
 
-    # prefill of 2,048 tokens, one sequence
-    toks = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
-    times = []
-    for i in range(args.warmup + 5):
-        slot = engine.start(1)
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        engine.step(slot, [toks], check=False)
-        stop.record()
-        torch.cuda.synchronize()
-        engine.finish(slot)
-        if i >= args.warmup:
-            times.append(start.elapsed_time(stop))
-    pre_ms = statistics.median(times)
+    prefill = time_prefill(engine, torch, rng, cfg, args.warmup, num, pk)
     T = PREFILL_TOKENS
-    flops = 2 * T * num["layer_params"] + 2 * num["head_params"] + num["n_attn"] * 2 * T * T * cfg.q_dim
-    prefill = {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
-               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # the same metric end to end through the public entry point: host token ids in and out every step
     prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).tolist()
@@ -243,6 +256,9 @@ def main() -> int:
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run only the first L layers (named in `config`)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure one part only (for profiling); the JSON line then lacks the other parts")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -90,11 +90,32 @@ def test_gemm_simt(k, dtype, M, N, K):
     close(res, ref + res0.double(), dtype, "gemm accumulate")
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (8, 6144, 2048), (5, 100, 8200), (16, 2048, 512), (9, 48, 64),
+                                   (33, 257, 1000), (64, 1030, 2048), (3, 65536 + 8, 256)])
+def test_gemm_skinny(k, M, N, K):
+    a = rnd((M, K), 5, torch.bfloat16).cuda()
+    w = rnd((N, K), 6, torch.bfloat16, 0.1).cuda()
+    bias = rnd((N,), 7, torch.float32).cuda()
+    ref = a.double() @ w.double().T
+    assert k.gemm_skinny_takes(a, w)
+    close(k.gemm_skinny(a, w), ref, torch.bfloat16, "skinny")
+    close(k.gemm_skinny(a, w, out_dtype=torch.float32), ref, torch.float32, "skinny f32 out")
+    close(k.gemm_skinny(a, w, bias=bias, out_dtype=torch.float32), ref + bias.double(), torch.float32, "skinny bias")
+    res = rnd((M, N), 8, torch.float32).cuda()
+    res0 = res.clone()
+    k.gemm_skinny(a, w, out=res, accumulate=True)
+    close(res, ref + res0.double(), torch.float32, "skinny accumulate")
+    assert not k.gemm_skinny_takes(rnd((65, K), 1, torch.bfloat16).cuda(), w)
+    assert not k.gemm_skinny_takes(rnd((2, 12), 1, torch.bfloat16).cuda(), rnd((4, 12), 1, torch.bfloat16).cuda())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
-    """A row's contraction is the same bits alone, in a batch, and at another place of it."""
+    """A row's contraction is the same bits alone, in a batch, and at another place of it, as long
+    as the same kernel runs: in float32 always, in bfloat16 among single-token-sized batches."""
     from zinfer_b200.parts.linear import linear
-    a = rnd((70, 96), 9, dtype).cuda()
+    rows = 70 if dtype == torch.float32 else 60
+    a = rnd((rows, 96), 9, dtype).cuda()
     w = rnd((200, 96), 10, dtype, 0.1).cuda()
     full = linear(a, w, out_dtype=torch.float32)
     one = linear(a[33:34].contiguous(), w, out_dtype=torch.float32)
@@ -222,7 +243,9 @@ class PagedSetup:
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,hd,page,n_rot,inter", [(4, 2, 16, 16, 16, False), (3, 1, 32, 32, 32, False),
                                                        (5, 5, 48, 64, 48, False), (8, 2, 80, 16, 40, True),
-                                                       (6, 2, 128, 64, 128, False), (20, 1, 64, 32, 64, False)])
+                                                       (6, 2, 128, 64, 128, False), (20, 1, 64, 32, 64, False),
+                                                       (32, 8, 64, 64, 64, False), (7, 7, 96, 32, 96, False),
+                                                       (16, 2, 32, 64, 32, False)])
 def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
     """Prompt step of unequal lengths into NaN-filled shuffled pages, then a single-token step
     with and without key splits, against whole-sequence references."""
@@ -252,7 +275,7 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
             q, kk, v = q.bfloat16().double(), kk.bfloat16().double(), v.bfloat16().double()
         return q, kk, v
 
-    def run(step_lens, starts, rows, num_splits=1, split_keys=0):
+    def run(step_lens, starts, rows, num_splits=1, split_keys=0, single_token=False):
         cu = np.concatenate([[0], np.cumsum(step_lens)]).astype(np.int32)
         tok_seq = torch.from_numpy(np.repeat(np.arange(len(step_lens)), step_lens).astype(np.int32)).cuda()
         tok_pos = torch.from_numpy(np.concatenate([np.arange(s, s + l) for s, l in zip(starts, step_lens)]).astype(np.int32)).cuda()
@@ -264,7 +287,7 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
         bq, _ = k.attn_tile_shape(H, Hkv)
         tiles = torch.from_numpy(attn_tiles_host(step_lens, bq)).cuda()
         return k.attention(q, setup.k, setup.v, tiles[0].contiguous(), tiles[1].contiguous(), cu_q, seq_start,
-                           seq_slot, setup.table_dev, H, Hkv, hd, scale, 0, num_splits, split_keys)
+                           seq_slot, setup.table_dev, H, Hkv, hd, scale, 0, num_splits, split_keys, single_token)
 
     out = run(lens, [0] * len(lens), torch.cat([s[:-1] for s in seqs]))
     assert status.item() == 0
@@ -281,6 +304,8 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
     ref = torch.cat(ref)
     close(run([1] * len(lens), lens, last), ref, dtype, "decode attention")
     close(run([1] * len(lens), lens, last, num_splits=3, split_keys=32), ref, dtype, "decode attention, 3 key chunks")
+    close(run([1] * len(lens), lens, last, single_token=True), ref, dtype, "single-token kernel")
+    close(run([1] * len(lens), lens, last, 2, 64, single_token=True), ref, dtype, "single-token kernel, 2 key chunks")
     assert not torch.isnan(out).any()
 
 
@@ -290,7 +315,7 @@ def test_attention_far_key_and_window_edge(k, dtype, window):
     """One key among hundreds is made to win the softmax; with a window the winner sits exactly
     on the window's first position for one query and one position outside it for the next."""
     from zinfer_b200.engine.context import attn_tiles_host
-    H, Hkv, hd, page = 4, 2, 32, 16
+    H, Hkv, hd, page = 4, 2, 32, 32
     T = 300
     scale = 1 / math.sqrt(hd)
     far = 7 if window == 0 else T - 2 - window + 1     # position of the key that must win
@@ -323,3 +348,10 @@ def test_attention_far_key_and_window_edge(k, dtype, window):
     if window:
         lost = torch.allclose(out[1].float().cpu().reshape(H, hd), v[far].float()[[h // g for h in range(H)]], atol=0.05)
         assert not lost, "a key outside the window was seen"
+    # the same two queries as single-token steps of two sequences that share the pages
+    table2 = setup.table_dev[[2, 2]].contiguous()
+    for splits, keys in ((1, 0), (4, 96)):
+        o2 = k.attention(q[-2:].reshape(2, H * hd).cuda(), setup.k, setup.v, i32([0, 1]), i32([0, 0]), i32([0, 1, 2]),
+                         i32([T - 2, T - 1]), i32([0, 1]), table2, H, Hkv, hd, scale, window, splits, keys,
+                         single_token=True)
+        close(o2, ref, dtype, f"single-token far key, window {window}, {splits} chunks")

@@ -31,10 +31,18 @@ _SIGNATURES = {
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
     },
+    "gemm_skinny": {
+        "zk_gemm_skinny": "ppppiiiiiiiip",
+        "zk_gemm_skinny_max_m": "",
+    },
     "shortconv": {
         "zk_conv_forward": "ppppppppiiilip",
         "zk_conv_state_update": "ppppiiilip",
         "zk_conv_decode": "ppppppiiilip",
+    },
+    "attention_decode": {
+        "zk_attn_decode": "ppppppppp" + "iiiiiiifiip",
+        "zk_attn_decode_takes": "iiii",
     },
     "sampling": {
         "zk_apply_penalties": "piipifppip",
@@ -200,6 +208,40 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def gemm_skinny_max_m() -> int:
+    return _fn("gemm_skinny", "zk_gemm_skinny_max_m")()
+
+
+def gemm_skinny_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `gemm_skinny` takes this contraction: bfloat16, few rows, 16-byte aligned rows."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and a.shape[0] <= gemm_skinny_max_m() and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+                accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias) for a [M <= 64, K] on the tensor cores, every weight read once."""
+    _need(a, "a", torch.bfloat16, (None, None))
+    _need(w, "w", torch.bfloat16, (None, a.shape[1]))
+    if not gemm_skinny_takes(a, w):
+        raise KernelError(f"gemm_skinny: a {tuple(a.shape)} / w {tuple(w.shape)} need M <= {gemm_skinny_max_m()}, "
+                          "K a multiple of 8 and 16-byte aligned rows")
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    _need(out, "out", (torch.float32, torch.bfloat16), (M, N))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (N,))
+    _check(_fn("gemm_skinny", "zk_gemm_skinny")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0),
+                                                w.stride(0), out.stride(0), dtype_code(out.dtype),
+                                                1 if accumulate else 0, _stream()), "gemm_skinny")
+    return out
+
+
 # ------------------------------------------------------------------------------- short convolution
 
 def conv_forward(bcx, state, w, bias, tok_seq, cu_q, seq_slot) -> torch.Tensor:
@@ -311,9 +353,12 @@ def attn_tile_shape(n_heads: int, n_kv: int) -> tuple[int, int]:
 
 
 def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, n_heads: int, n_kv: int,
-              head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0) -> torch.Tensor:
+              head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0,
+              single_token: bool = False) -> torch.Tensor:
     """Causal grouped-query attention of a packed batch against the paged cache.  With
-    num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards."""
+    num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
+    `single_token` says that every sequence brings exactly one query (row b = sequence b); the
+    bfloat16 kernel for that case is used when it takes the sizes."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
     n = q.shape[0]
     for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
@@ -330,6 +375,16 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if num_splits > 1:
         part_o = torch.empty((num_splits, n * n_heads, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
+    if (single_token and q.dtype == torch.bfloat16
+            and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size)):
+        _check(_fn("attention_decode", "zk_attn_decode")(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
+            _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
+            scale, num_splits, split_keys, _stream()), "attention (single token)")
+        if num_splits > 1:
+            _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
+                                                     num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+        return out
     _check(_fn("attention", "zk_attn_fwd")(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
         _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,

@@ -89,7 +89,7 @@ class GqaAttention(Mixer):
         num_splits, split_keys = ctx.kv_splits(self.n_kv)
         att = kernels.attention(q, kv.k, kv.v, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot,
                                 kv.page_table, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
-                                num_splits, split_keys)
+                                num_splits, split_keys, single_token=ctx.is_decode)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 
