@@ -29,7 +29,7 @@ def test_every_signature_matches_its_prototype():
     for lib, funcs in kernels._SIGNATURES.items():
         text = (CSRC / f"{lib}.cu").read_text()
         for name, sig in funcs.items():
-            m = re.search(r"\bint\s+" + name + r"\s*\(([^)]*)\)\s*\{", text)
+            m = re.search(r"\b(?:int|long long)\s+" + name + r"\s*\(([^)]*)\)\s*\{", text)
             assert m, f"{name} not found in {lib}.cu"
             assert c_kinds(m.group(1)) == sig, f"{name}: C has {c_kinds(m.group(1))}, Python has {sig}"
             checked += 1
@@ -38,6 +38,6 @@ def test_every_signature_matches_its_prototype():
 
 def test_every_exported_launcher_has_a_signature():
     for cu in CSRC.glob("*.cu"):
-        exported = set(re.findall(r"\bint\s+(zk_\w+)\s*\(", cu.read_text()))
+        exported = set(re.findall(r"\b(?:int|long long)\s+(zk_\w+)\s*\(", cu.read_text()))
         known = set(kernels._SIGNATURES.get(cu.stem, {}))
         assert exported <= known, f"{cu.name}: {sorted(exported - known)} have no ctypes signature"

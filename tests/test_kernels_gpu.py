@@ -109,6 +109,102 @@ def test_gemm_skinny(k, M, N, K):
     assert not k.gemm_skinny_takes(rnd((2, 12), 1, torch.bfloat16).cuda(), rnd((4, 12), 1, torch.bfloat16).cuda())
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 331 * 8, 2048), (2048, 6144, 2048), (130, 264, 8200),
+                                   (65, 16, 72), (300, 2048, 8192)])
+def test_gemm_tc_prompt_shapes(k, M, N, K):
+    a = rnd((M, K), 5, torch.bfloat16).cuda()
+    w = rnd((N, K), 6, torch.bfloat16, 0.1).cuda()
+    bias = rnd((N,), 7, torch.float32).cuda()
+    ref = a.double() @ w.double().T
+    assert k.gemm_tc_takes(a, w)
+    close(k.gemm_tc(a, w, out_dtype=torch.float32), ref, torch.float32, "tc f32 out")
+    close(k.gemm_tc(a, w), ref, torch.bfloat16, "tc bf16 out")
+    close(k.gemm_tc(a, w, bias=bias, out_dtype=torch.float32), ref + bias.double(), torch.float32, "tc bias")
+    res = rnd((M, N), 8, torch.float32).cuda()
+    res0 = res.clone()
+    k.gemm_tc(a, w, out=res, accumulate=True)
+    close(res, ref + res0.double(), torch.float32, "tc accumulate")
+    assert k.status_word("cuda").item() == 0
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 6144, 2048, 1), (8, 2048, 8192, 8), (16, 331 * 8, 2048, 3),
+                                          (17, 2048, 2048, 4), (33, 100, 520, 2), (64, 16384, 2048, 2), (5, 65536, 256, 1)])
+def test_gemm_tc_single_token_shapes(k, M, N, K, splits):
+    a = rnd((M, K), 5, torch.bfloat16).cuda()
+    w = rnd((N, K), 6, torch.bfloat16, 0.1).cuda()
+    bias = rnd((N,), 7, torch.float32).cuda()
+    ref = a.double() @ w.double().T
+    close(k.gemm_tc(a, w, out_dtype=torch.float32, splits=splits), ref, torch.float32, "tc swapped")
+    close(k.gemm_tc(a, w, splits=splits, bias=bias), ref + bias.double(), torch.bfloat16, "tc swapped bf16 + bias")
+    res = rnd((M, N), 8, torch.float32).cuda()
+    res0 = res.clone()
+    k.gemm_tc(a, w, out=res, accumulate=True, splits=splits)
+    close(res, ref + res0.double(), torch.float32, "tc swapped accumulate")
+    again = res0.clone()
+    k.gemm_tc(a, w, out=again, accumulate=True, splits=splits)
+    assert torch.equal(again, res), "the same launch gave other bits"
+    assert k.status_word("cuda").item() == 0
+
+
+def norm_ref(x, w, eps):
+    return (x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * w.double())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (8, 6144, 2048), (16, 100, 1000), (11, 48, 64)])
+def test_gemm_skinny_with_fused_norm(k, M, N, K):
+    x = rnd((M, K), 1, torch.float32, 3.0).cuda()
+    nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
+    w = rnd((N, K), 3, torch.bfloat16, 0.1).cuda()
+    ref = norm_ref(x, nw, 1e-5).bfloat16().double() @ w.double().T
+    inp = k.NormInput(x, nw, 1e-5)
+    assert k.gemm_skinny_takes(inp, w)
+    close(k.gemm_skinny(inp, w, out_dtype=torch.float32), ref, torch.bfloat16, "skinny + norm")
+    unfused = k.gemm_skinny(k.rmsnorm(x, nw, 1e-5, torch.bfloat16), w, out_dtype=torch.float32)
+    close(k.gemm_skinny(inp, w, out_dtype=torch.float32), unfused.double(), torch.bfloat16, "fused vs unfused norm")
+    assert not k.gemm_skinny_takes(k.NormInput(rnd((17, K), 1, torch.float32).cuda(), nw, 1e-5), w)
+
+
+@pytest.mark.parametrize("M,F,K,norm", [(1, 200, 80, False), (8, 8192, 2048, True), (16, 136, 96, True), (5, 17, 64, False)])
+def test_gemm_skinny_swiglu(k, M, F, K, norm):
+    w = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
+    if norm:
+        x = rnd((M, K), 1, torch.float32, 2.0).cuda()
+        nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
+        inp, a = k.NormInput(x, nw, 1e-6), norm_ref(x, nw, 1e-6).bfloat16().double()
+    else:
+        inp = rnd((M, K), 1, torch.bfloat16).cuda()
+        a = inp.double()
+    g, u = a @ w[:F].double().T, a @ w[F:].double().T
+    close(k.gemm_skinny_swiglu(inp, w), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "skinny swiglu")
+
+
+@pytest.mark.parametrize("M,D,K,taps,bias,norm", [(1, 80, 80, 2, False, False), (8, 2048, 2048, 3, False, True),
+                                                  (13, 96, 96, 4, True, True), (16, 40, 64, 7, True, False)])
+def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
+    """Three fused single-token steps against in_proj + conv_decode, state included."""
+    w_in = rnd((3 * D, K), 3, torch.bfloat16, 0.2).cuda()
+    tw = rnd((taps, D), 4, torch.float32).cuda()
+    in_b = rnd((3 * D,), 5, torch.float32).cuda() if bias else None
+    cb = rnd((D,), 6, torch.float32).cuda() if bias else None
+    nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
+    slots = torch.randperm(M + 3, generator=torch.Generator().manual_seed(1))[:M].to(torch.int32).cuda()
+    st_a = rnd((M + 3, taps - 1, D), 7, torch.float32).cuda()
+    st_b = st_a.clone()
+    for step in range(3):
+        x = rnd((M, K), 10 + step, torch.float32, 2.0).cuda()
+        if norm:
+            inp, xn = k.NormInput(x, nw, 1e-5), k.rmsnorm(x, nw, 1e-5, torch.bfloat16)
+        else:
+            inp = xn = x.bfloat16()
+        y_fused = k.gemm_skinny_conv(inp, w_in, in_b, st_a, tw, cb, slots)
+        bcx = k.gemm_skinny(xn, w_in, bias=in_b)
+        y_ref = k.conv_decode(bcx, st_b, tw, cb, slots)
+        close(y_fused, y_ref.double(), torch.bfloat16, f"fused conv step {step}")
+        close(st_a, st_b.double(), torch.bfloat16, f"fused conv state {step}")
+    untouched = [i for i in range(M + 3) if i not in slots.cpu().tolist()]
+    assert torch.equal(st_a[untouched], rnd((M + 3, taps - 1, D), 7, torch.float32).cuda()[untouched])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
     """A row's contraction is the same bits alone, in a batch, and at another place of it, as long

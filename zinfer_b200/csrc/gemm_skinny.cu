@@ -5,16 +5,44 @@
 // The roles are swapped against the usual layout: 16 weight rows are the M side of
 // mma.m16n8k16 and 8 tokens its N side.  A lane loads 16 contiguous bytes (8 bfloat16) of a
 // weight row and of a token row and feeds them to two MMAs; both operands use the same
-// permutation of k inside a 32-wide slab, which a dot product does not see.  A block owns
-// 16*RG weight rows; its 8 warps split K between them and their partial sums are added in warp
-// order through shared memory, so a result depends neither on M nor on the token's place in
-// the batch.  (Reference: one dot product per weight row and token, src/model.zig:923-1026;
-// bfloat16 dot with float32 accumulation, src/quant.zig:444-455.)
+// permutation of k inside a 32-wide slab, which a dot product does not see.  A block owns RG
+// groups of 16 weight rows; its 8 warps split K between them and their partial sums are added
+// in warp order through shared memory, so a result depends neither on M nor on the token's
+// place in the batch.  (Reference: one dot product per weight row and token,
+// src/model.zig:923-1026; bfloat16 dot with float32 accumulation, src/quant.zig:444-455.)
+//
+// What is fused around the contraction, because at these sizes a kernel launch costs as much
+// as the kernel:
+//  * NORM: X is the float32 residual stream and the block applies RMSNorm itself
+//    (src/model.zig:1166-1181) while its first weights are in flight;
+//  * EPI_SWIGLU: the block owns gate rows f and up rows F + f and writes silu(g) * u
+//    (src/model.zig:1085-1117: gate, up and the activation in one worker);
+//  * EPI_CONV: the block owns rows ch, D + ch, 2D + ch of the short convolution's in_proj and
+//    runs the gated convolution with its state update on them (src/model.zig:2002-2020).
 #include "common.cuh"
 
 namespace {
 
 constexpr int WARPS = 8;
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_CONV = 2 };
+
+struct Args {
+  const bf16* X;         // [M, K] bfloat16, or null when Xf is given
+  const float* Xf;       // [M, K] float32 residual rows to be normalised (NORM)
+  const float* norm_w;   // [K]
+  float eps;
+  const bf16* W;         // [rows, K]
+  void* C;
+  const float* bias;     // per weight row, or null
+  int M, N, K, ldx, ldw, ldc, accumulate;
+  // EPI_CONV
+  float* conv_state;     // [slots, taps-1, N] float32
+  const float* conv_taps;  // [taps, N]
+  const float* conv_bias;  // [N] or null
+  const int* seq_slot;   // [M]
+  int taps;
+  long long state_stride;
+};
 
 __device__ __forceinline__ void mma16816(float c[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
@@ -32,22 +60,107 @@ __device__ __forceinline__ uint4 ld16_stream(const bf16* p) {
                : "l"(p));
   return v;
 }
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const unsigned*>(&t);
+}
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 // RG: groups of 16 weight rows per block; NT: groups of 8 tokens; UNROLL: 32-wide k slabs whose
-// loads are all issued before their MMAs (what keeps enough bytes in flight).
-template <int RG, int NT, int UNROLL, typename TC>
-__global__ void __launch_bounds__(WARPS * 32)
-    skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TC* __restrict__ C,
-                  const float* __restrict__ bias, int M, int N, int K, int ldx, int ldw, int ldc, int accumulate) {
-  __shared__ float red[WARPS][RG * 16][NT * 8 + 1];
+// weight loads are in flight together.  N is the number of output columns; for EPI_PLAIN weight
+// row = column, for the fused epilogues group r holds weight rows r*N + column.
+template <int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
+__global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
+  extern __shared__ float smem[];
+  constexpr int RED_LD = NT * 8 + 1;
+  float(*red)[RG * 16][RED_LD] = reinterpret_cast<float(*)[RG * 16][RED_LD]>(smem);
+  float* row_scale = smem + WARPS * RG * 16 * RED_LD;  // [NT * 8], then [NT * 8][WARPS] partial sums
+  bf16* xs = reinterpret_cast<bf16*>(smem + ((WARPS * RG * 16 * RED_LD + NT * 8 + NT * 8 * WARPS + 3) / 4) * 4);  // NORM: [NT * 8][K + 8] bfloat16
+
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int n0 = blockIdx.x * (16 * RG);
+  const int M = a.M, N = a.N, K = a.K;
+  const int n0 = blockIdx.x * (EPI == EPI_PLAIN ? 16 * RG : 16);
 
-  // this warp's slice of K, in slabs of 32
   const int slabs = (K + 31) / 32;
   const int per = (slabs + WARPS - 1) / WARPS;
   const int s_begin = warp * per, s_end = min(slabs, s_begin + per);
+
+  const bf16* wrow[RG][2];
+  bool wok[RG][2];
+#pragma unroll
+  for (int r = 0; r < RG; ++r)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int col = n0 + (EPI == EPI_PLAIN ? r * 16 : 0) + g + 8 * h;
+      wok[r][h] = col < N;
+      const size_t row = (EPI == EPI_PLAIN ? 0 : (size_t)r * N) + (wok[r][h] ? col : 0);
+      wrow[r][h] = a.W + row * a.ldw;
+    }
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+
+  uint4 wv[UNROLL][RG][2];
+  auto load_w = [&](int s) {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (s + u) * 32 + 8 * c;
+      const bool kok = (s + u) < s_end && k < K;  // K % 8 == 0: a 16-byte piece is all in or all out
+#pragma unroll
+      for (int r = 0; r < RG; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) wv[u][r][h] = (kok && wok[r][h]) ? ld16_stream(wrow[r][h] + k) : zero;
+    }
+  };
+  load_w(s_begin);  // the first weights are under way while the norm is computed
+
+  // NORM: the block normalises the M rows once into shared memory as bfloat16 (row stride padded
+  // by 16 bytes so that the 8 rows a fragment load touches fall into different banks).
+  const int xs_ld = K + 8;
+  if constexpr (NORM) {
+    float* part = row_scale + NT * 8;  // [NT * 8][WARPS] partial sums of squares
+    for (int m0 = 0; m0 < M; m0 += 4) {
+      float ss[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          v[j] = (m0 + j < M) ? *reinterpret_cast<const float4*>(a.Xf + (size_t)(m0 + j) * a.ldx + k)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ss[j] = fmaf(v[j].x, v[j].x, ss[j]);
+          ss[j] = fmaf(v[j].y, v[j].y, ss[j]);
+          ss[j] = fmaf(v[j].z, v[j].z, ss[j]);
+          ss[j] = fmaf(v[j].w, v[j].w, ss[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float t = warp_sum(ss[j]);
+        if (lane == 0 && m0 + j < M) part[(m0 + j) * WARPS + warp] = t;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < M) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) t += part[threadIdx.x * WARPS + w];
+      row_scale[threadIdx.x] = 1.0f / sqrtf(t / (float)K + a.eps);
+    }
+    __syncthreads();
+    for (int m = 0; m < M; ++m) {
+      const float sc = row_scale[m];
+      for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(a.Xf + (size_t)m * a.ldx + k);
+        const float4 w = *reinterpret_cast<const float4*>(a.norm_w + k);
+        uint2 pk;
+        pk.x = pack2((v.x * sc) * w.x, (v.y * sc) * w.y);
+        pk.y = pack2((v.z * sc) * w.z, (v.w * sc) * w.w);
+        *reinterpret_cast<uint2*>(xs + (size_t)m * xs_ld + k) = pk;
+      }
+    }
+    __syncthreads();
+  }
 
   float acc[RG][NT][4];
 #pragma unroll
@@ -57,38 +170,26 @@ __global__ void __launch_bounds__(WARPS * 32)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[r][t][i] = 0.f;
 
-  const bf16* wrow[RG][2];
-  bool wok[RG][2];
-#pragma unroll
-  for (int r = 0; r < RG; ++r)
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int n = n0 + r * 16 + g + 8 * h;
-      wok[r][h] = n < N;
-      wrow[r][h] = W + (size_t)(wok[r][h] ? n : 0) * ldw;
-    }
-  const bf16* xrow[NT];
   bool xok[NT];
 #pragma unroll
-  for (int t = 0; t < NT; ++t) {
-    const int m = t * 8 + g;
-    xok[t] = m < M;
-    xrow[t] = X + (size_t)(xok[t] ? m : 0) * ldx;
-  }
-  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int t = 0; t < NT; ++t) xok[t] = t * 8 + g < M;
 
   for (int s = s_begin; s < s_end; s += UNROLL) {
-    uint4 wv[UNROLL][RG][2], xv[UNROLL][NT];
+    uint4 xv[UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (s + u) * 32 + 8 * c;
-      const bool kok = (s + u) < s_end && k < K;  // K % 8 == 0, so a 16-byte piece is all in or all out
+      const bool kok = (s + u) < s_end && k < K;
 #pragma unroll
-      for (int r = 0; r < RG; ++r)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) wv[u][r][h] = (kok && wok[r][h]) ? ld16_stream(wrow[r][h] + k) : zero;
-#pragma unroll
-      for (int t = 0; t < NT; ++t) xv[u][t] = (kok && xok[t]) ? ld16(xrow[t] + k) : zero;
+      for (int t = 0; t < NT; ++t) {
+        if (!(kok && xok[t])) {
+          xv[u][t] = zero;
+        } else if constexpr (NORM) {
+          xv[u][t] = *reinterpret_cast<const uint4*>(xs + (size_t)(t * 8 + g) * xs_ld + k);
+        } else {
+          xv[u][t] = ld16(a.X + (size_t)(t * 8 + g) * a.ldx + k);
+        }
+      }
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
@@ -99,6 +200,7 @@ __global__ void __launch_bounds__(WARPS * 32)
           mma16816(acc[r][t], wv[u][r][0].x, wv[u][r][1].x, wv[u][r][0].y, wv[u][r][1].y, xv[u][t].x, xv[u][t].y);
           mma16816(acc[r][t], wv[u][r][0].z, wv[u][r][1].z, wv[u][r][0].w, wv[u][r][1].w, xv[u][t].z, xv[u][t].w);
         }
+    if (s + UNROLL < s_end) load_w(s + UNROLL);
   }
 
   // partial sums of the 8 warps -> shared memory; C fragment: rows g, g+8; columns 2c, 2c+1
@@ -112,40 +214,116 @@ __global__ void __launch_bounds__(WARPS * 32)
       red[warp][r * 16 + g + 8][t * 8 + 2 * c + 1] = acc[r][t][3];
     }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < RG * 16 * NT * 8; idx += WARPS * 32) {
-    const int m = idx / (RG * 16), nl = idx % (RG * 16);
-    const int n = n0 + nl;
-    if (m >= M || n >= N) continue;
+
+  auto total = [&](int row, int m) {
     float v = 0.f;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) v += red[w][nl][m];
-    if (bias) v += bias[n];
-    TC* dst = C + (size_t)m * ldc + n;
-    if (accumulate) v += to_f32(*dst);
-    *dst = from_f32<TC>(v);
+    for (int w = 0; w < WARPS; ++w) v += red[w][row][m];
+    return v;
+  };
+
+  if constexpr (EPI == EPI_PLAIN) {
+    TC* C = reinterpret_cast<TC*>(a.C);
+    for (int idx = threadIdx.x; idx < RG * 16 * NT * 8; idx += WARPS * 32) {
+      const int m = idx / (RG * 16), nl = idx % (RG * 16);
+      const int n = n0 + nl;
+      if (m >= M || n >= N) continue;
+      float v = total(nl, m);
+      if (a.bias) v += a.bias[n];
+      TC* dst = C + (size_t)m * a.ldc + n;
+      if (a.accumulate) v += to_f32(*dst);
+      *dst = from_f32<TC>(v);
+    }
+  } else if constexpr (EPI == EPI_SWIGLU) {
+    bf16* C = reinterpret_cast<bf16*>(a.C);
+    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += WARPS * 32) {
+      const int m = idx / 16, i = idx % 16;
+      const int n = n0 + i;
+      if (m >= M || n >= N) continue;
+      const float gate = total(i, m), up = total(16 + i, m);
+      C[(size_t)m * a.ldc + n] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+    }
+  } else {  // EPI_CONV: token m is sequence m
+    bf16* C = reinterpret_cast<bf16*>(a.C);
+    const int taps = a.taps;
+    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += WARPS * 32) {
+      const int m = idx / 16, i = idx % 16;
+      const int ch = n0 + i;
+      if (m >= M || ch >= N) continue;
+      float bv = total(i, m), cv = total(16 + i, m), xval = total(32 + i, m);
+      if (a.bias) {
+        bv += a.bias[ch];
+        cv += a.bias[N + ch];
+        xval += a.bias[2 * N + ch];
+      }
+      // rounded as the unfused path stores them, so both paths keep the same state
+      const float u_new = round_bf16(bv) * round_bf16(xval);
+      float* st = a.conv_state + (size_t)a.seq_slot[m] * a.state_stride;
+      float sum = 0.f;
+      for (int k = 0; k < taps - 1; ++k) {
+        const float u = st[(size_t)k * N + ch];
+        sum = fmaf(a.conv_taps[(size_t)k * N + ch], u, sum);
+        if (k > 0) st[(size_t)(k - 1) * N + ch] = u;
+      }
+      sum = fmaf(a.conv_taps[(size_t)(taps - 1) * N + ch], u_new, sum);
+      st[(size_t)(taps - 2) * N + ch] = u_new;
+      if (a.conv_bias) sum += a.conv_bias[ch];
+      C[(size_t)m * a.ldc + ch] = __float2bfloat16_rn(round_bf16(cv) * sum);
+    }
   }
 }
 
-template <int RG, int NT, int UNROLL, typename TC>
-int launch(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
-           int accumulate, cudaStream_t stream) {
-  const int grid = ceil_div_i(N, 16 * RG);
-  skinny_kernel<RG, NT, UNROLL, TC><<<grid, WARPS * 32, 0, stream>>>((const bf16*)X, (const bf16*)W, (TC*)C, bias, M, N, K, ldx,
-                                                             ldw, ldc, accumulate);
+template <int RG, int NT>
+size_t smem_bytes(bool norm, int K) {
+  size_t floats = (size_t)WARPS * RG * 16 * (NT * 8 + 1) + NT * 8 + NT * 8 * WARPS;
+  floats = (floats + 3) / 4 * 4;  // the bfloat16 rows start 16-byte aligned
+  return sizeof(float) * floats + (norm ? sizeof(bf16) * (size_t)NT * 8 * (K + 8) : 0);
+}
+
+template <int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
+int launch(const Args& a, cudaStream_t stream) {
+  auto kern = skinny_kernel<RG, NT, UNROLL, EPI, NORM, TC>;
+  const size_t smem = smem_bytes<RG, NT>(NORM, a.K);
+  if (smem > 200 * 1024) return ZK_EINVAL;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int grid = ceil_div_i(a.N, EPI == EPI_PLAIN ? 16 * RG : 16);
+  kern<<<grid, WARPS * 32, smem, stream>>>(a);
   return ZK_LAUNCH_STATUS();
 }
 
-template <typename TC>
-int dispatch(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
-             int accumulate, cudaStream_t stream) {
-  // rows per block: 16 while that still gives every SM a few blocks, else 32
-  const bool wide = N >= 16 * 148 * 8;
-  if (M <= 8) return wide ? launch<2, 1, 4, TC>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream)
-                          : launch<1, 1, 4, TC>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream);
-  if (M <= 16) return wide ? launch<2, 2, 4, TC>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream)
-                           : launch<1, 2, 4, TC>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream);
-  if (M <= 32) return launch<2, 4, 2, TC>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream);
-  return launch<1, 8, 2, TC>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream);
+template <bool NORM, typename TC>
+int dispatch_plain(const Args& a, cudaStream_t stream) {
+  const bool wide = a.N >= 16 * 148 * 8;  // 32 rows per block once 16 would give every SM many blocks
+  if (a.M <= 8) return wide ? launch<2, 1, 4, EPI_PLAIN, NORM, TC>(a, stream) : launch<1, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
+  if (a.M <= 16) return wide ? launch<2, 2, 4, EPI_PLAIN, NORM, TC>(a, stream) : launch<1, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
+  if constexpr (NORM) {
+    return ZK_EINVAL;
+  } else {
+    if (a.M <= 32) return launch<2, 4, 2, EPI_PLAIN, false, TC>(a, stream);
+    return launch<1, 8, 2, EPI_PLAIN, false, TC>(a, stream);
+  }
+}
+
+template <int RG, int EPI>
+int dispatch_fused(const Args& a, cudaStream_t stream) {
+  const bool norm = a.Xf != nullptr;
+  if (a.M <= 8) return norm ? launch<RG, 1, 4, EPI, true, bf16>(a, stream) : launch<RG, 1, 4, EPI, false, bf16>(a, stream);
+  if (a.M <= 16) return norm ? launch<RG, 2, 2, EPI, true, bf16>(a, stream) : launch<RG, 2, 2, EPI, false, bf16>(a, stream);
+  return ZK_EINVAL;
+}
+
+int check_common(const Args& a, int max_m) {
+  if (a.M > max_m || a.K <= 0 || a.K % 8 || a.ldw % 8 || a.ldw < a.K || a.ldx < a.K) return ZK_EINVAL;
+  if ((uintptr_t)a.W % 16) return ZK_EINVAL;
+  if (a.Xf) {
+    if (a.ldx % 4 || (uintptr_t)a.Xf % 16 || (uintptr_t)a.norm_w % 16 || !a.norm_w) return ZK_EINVAL;
+  } else {
+    if (!a.X || a.ldx % 8 || (uintptr_t)a.X % 16) return ZK_EINVAL;
+  }
+  return 0;
 }
 
 }  // namespace
@@ -153,16 +331,49 @@ int dispatch(const void* X, const void* W, void* C, const float* bias, int M, in
 extern "C" {
 
 int zk_gemm_skinny_max_m() { return 64; }
+int zk_gemm_skinny_fused_max_m() { return 16; }
 
-// X [M, K], W [N, K] bfloat16 with K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
-int zk_gemm_skinny(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw,
-                   int ldc, int out_dtype, int accumulate, cudaStream_t stream) {
+// X [M, K] bfloat16 (or Xf [M, K] float32 + norm_w [K], eps: RMSNorm fused, M <= 16), W [N, K]
+// bfloat16 with K % 8 == 0 and 16-byte aligned rows; C [M, N] bfloat16 or float32.
+int zk_gemm_skinny(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* C,
+                   const float* bias, int M, int N, int K, int ldx, int ldw, int ldc, int out_dtype, int accumulate,
+                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < N) return ZK_EINVAL;
-  if (((uintptr_t)X | (uintptr_t)W) % 16) return ZK_EINVAL;
-  if (out_dtype == ZK_F32) return dispatch<float>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream);
-  if (out_dtype == ZK_BF16) return dispatch<bf16>(X, W, C, bias, M, N, K, ldx, ldw, ldc, accumulate, stream);
+  Args a{};
+  a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = C; a.bias = bias;
+  a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldc; a.accumulate = accumulate;
+  if (ldc < N || check_common(a, Xf ? 16 : 64)) return ZK_EINVAL;
+  if (out_dtype == ZK_F32) return Xf ? dispatch_plain<true, float>(a, stream) : dispatch_plain<false, float>(a, stream);
+  if (out_dtype == ZK_BF16) return Xf ? dispatch_plain<true, bf16>(a, stream) : dispatch_plain<false, bf16>(a, stream);
   return ZK_EINVAL;
+}
+
+// h[M, F] = silu(x W_gate^T) * (x W_up^T), W = [gate rows; up rows] of shape [2F, K]; M <= 16.
+int zk_gemm_skinny_swiglu(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* H,
+                          int M, int F, int K, int ldx, int ldw, int ldh, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  Args a{};
+  a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = H;
+  a.M = M; a.N = F; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldh;
+  if (ldh < F || check_common(a, 16)) return ZK_EINVAL;
+  return dispatch_fused<2, EPI_SWIGLU>(a, stream);
+}
+
+// Single-token step of the short convolution: [B, C, X] = x W_in^T (+ bias), u = B*X, the causal
+// convolution over the slot's state, y = C * conv, state shifted by one.  Token m is sequence m.
+// W [3D, K]; state [slots, taps-1, D] float32; taps [taps, D]; y [M, D] bfloat16; M <= 16.
+int zk_gemm_skinny_conv(const void* X, const float* Xf, const float* norm_w, float eps, const void* W,
+                        const float* in_bias, float* state, const float* taps_w, const float* conv_bias,
+                        const int* seq_slot, void* Y, int M, int D, int K, int taps, int ldx, int ldw, int ldy,
+                        long long state_stride, cudaStream_t stream) {
+  if (M <= 0 || D <= 0) return 0;
+  Args a{};
+  a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = Y; a.bias = in_bias;
+  a.M = M; a.N = D; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldy;
+  a.conv_state = state; a.conv_taps = taps_w; a.conv_bias = conv_bias; a.seq_slot = seq_slot; a.taps = taps;
+  a.state_stride = state_stride;
+  if (ldy < D || taps < 2 || !state || !taps_w || !seq_slot || check_common(a, 16)) return ZK_EINVAL;
+  return dispatch_fused<3, EPI_CONV>(a, stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,433 @@
+// C[M, N] (+)= X[M, K] . W[N, K]^T (+ bias) on the fifth-generation tensor cores of sm_100a.
+//
+// One block computes one 128 x BN tile of the product of two K-major bfloat16 operands:
+//   * warp 0 (one lane) is the producer: per 64-wide k block it issues two TMA tile loads
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle) into a ring of shared-memory stages and arms
+//     the stage's mbarrier with the byte count;
+//   * warp 1 allocates the tile's accumulator in tensor memory and (one lane) issues
+//     tcgen05.mma.kind::f16 -- four k=16 steps per stage -- then tcgen05.commit, which frees the
+//     stage when the MMAs have read it, and finally signals the accumulator as complete;
+//   * warps 2..5 are the epilogue: each reads its quarter of the accumulator's 128 lanes with
+//     tcgen05.ld and stores the tile with bias / residual add / conversion.
+// Two roles of the operands:
+//   normal : rows of the tile are tokens (X), columns are weight rows (W): prompt steps;
+//   swapped: rows of the tile are weight rows, columns are the few tokens of a single-token
+//            step (16..64): every weight is read once, and K may be split over blockIdx.z so
+//            that all SMs stream; partial tiles go through a float32 workspace and the block
+//            that arrives last adds them in split order (no atomics on data, same bits each run).
+// Accumulation is float32 in tensor memory.  (Reference: the matmul driver with its accumulate
+// flag, src/model.zig:903-1026, 918-920.)
+//
+// Every wait on an mbarrier is bounded: after about two seconds the block records a code in
+// *status, stops issuing work, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;          // tile rows = accumulator lanes
+constexpr int BK = 64;           // k block: 64 bfloat16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;     // producer warp, MMA warp, four epilogue warps
+constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds of SM clock
+
+struct Params {
+  void* C;
+  const float* bias;
+  float* workspace;    // swapped with splits: [tiles][splits][BN][128] float32
+  unsigned* tickets;   // [tiles], zero before the launch and zero again after it
+  int* status;
+  int M, N, K;         // M tokens, N weight rows
+  int ldc, accumulate, splits;
+};
+
+// ------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false = gave up after WAIT_CYCLES.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// 16 consecutive float32 columns of this thread's accumulator lane
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float v[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), version 1, swizzle mode 2.
+__device__ __forceinline__ unsigned long long smem_desc(const void* tile) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_u32(tile) & 0x3FFFF) >> 4);   // start address
+  d |= (unsigned long long)1 << 16;                             // leading byte offset (unused with swizzle)
+  d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset
+  d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
+  d |= (unsigned long long)2 << 61;                             // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, shape M x N.
+__device__ __forceinline__ unsigned instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct Smem {
+  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr size_t BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// SWAP = false: A tiles are 128 tokens of X, B tiles are BN weight rows; C[token][weight row].
+// SWAP = true : A tiles are 128 weight rows, B tile is the BN-padded token block.
+template <int BN, int STAGES, bool SWAP, typename TC>
+__global__ void __launch_bounds__(THREADS)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  using S = Smem<BN, STAGES>;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(tiles + (size_t)STAGES * S::STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_done = empty + STAGES;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_done + 1);
+  volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned* last_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a_tile = blockIdx.x, b_tile = blockIdx.y, split = blockIdx.z;
+  constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+
+  const int nkb = (p.K + BK - 1) / BK;
+  const int per = (nkb + p.splits - 1) / p.splits;
+  const int kb0 = split * per, kb1 = min(nkb, kb0 + per);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_done, 1);
+    *aborted = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+      const int s = it % STAGES;
+      if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+        atomicExch(p.status, 11);
+        *aborted = 1;
+        break;
+      }
+      if (*aborted) break;
+      unsigned char* a_dst = tiles + (size_t)s * S::STAGE_BYTES;
+      mbar_expect_tx(&full[s], S::STAGE_BYTES);
+      tma_load_2d(a_dst, &map_a, kb * BK, a_tile * BM, &full[s]);
+      tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN, &full[s]);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer
+    const unsigned idesc = instr_desc(BM, BN);
+    bool ok = true;
+    for (int kb = kb0, it = 0; kb < kb1 && ok; ++kb, ++it) {
+      const int s = it % STAGES;
+      if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
+        atomicExch(p.status, 12);
+        *aborted = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const unsigned char* a_src = tiles + (size_t)s * S::STAGE_BYTES;
+      const unsigned long long da = smem_desc(a_src), db = smem_desc(a_src + S::A_BYTES);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along the swizzled row per step
+        umma_bf16(tmem_base, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
+                  (it > 0 || k > 0) ? 1u : 0u);
+      umma_commit(&empty[s]);
+    }
+    umma_commit(acc_done);  // arrives when every MMA above has finished (at once if none was issued)
+  } else if (warp >= 2) {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;            // the 32 accumulator lanes this warp may read
+    const int row = quarter * 32 + lane;     // row of the tile
+    bool ok = mbar_wait(acc_done, 0);
+    if (!ok) {
+      if (lane == 0) atomicExch(p.status, 13);
+      *aborted = 1;
+    }
+    ok = ok && !*aborted && kb1 > kb0;
+    tc_fence_after();
+    const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+
+    if constexpr (!SWAP) {
+      const int m = a_tile * BM + row;
+      TC* crow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (ok) tmem_ld16(lane_addr + c0, v);   // warp-collective: every lane of the warp takes part
+        const int n0 = b_tile * BN + c0;
+        if (!ok || m >= p.M || n0 >= p.N) continue;
+        if (n0 + 16 <= p.N && (p.ldc % 8) == 0) {
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += p.bias[n0 + j];
+          }
+          if constexpr (sizeof(TC) == 4) {
+            float4* dst = reinterpret_cast<float4*>(crow + n0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (p.accumulate) {
+                const float4 old = dst[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              dst[j] = o;
+            }
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(crow + n0);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              float w[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) w[i] = v[8 * j + i];
+              if (p.accumulate) {
+                const uint4 old = dst[j];
+                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  w[2 * i] += __low2float(ob[i]);
+                  w[2 * i + 1] += __high2float(ob[i]);
+                }
+              }
+              uint4 o;
+              __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(w[2 * i], w[2 * i + 1]);
+              dst[j] = o;
+            }
+          }
+        } else {
+          for (int j = 0; j < 16 && n0 + j < p.N; ++j) {
+            float o = v[j] + (p.bias ? p.bias[n0 + j] : 0.f);
+            if (p.accumulate) o += to_f32(crow[n0 + j]);
+            crow[n0 + j] = from_f32<TC>(o);
+          }
+        }
+      }
+    } else {
+      // rows are weight rows n, columns are tokens; a warp's lanes are 32 consecutive n
+      const int n = a_tile * BM + row;
+      TC* C = reinterpret_cast<TC*>(p.C);
+      const int tile_id = a_tile;
+      float* part = p.splits > 1 ? p.workspace + ((size_t)tile_id * p.splits + split) * (BN * BM) : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (ok) {
+          tmem_ld16(lane_addr + c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+        if (p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * BM + row] = v[j];
+        } else if (n < p.N) {
+          const float b = p.bias ? p.bias[n] : 0.f;
+          for (int j = 0; j < 16 && c0 + j < p.M; ++j) {
+            TC* dst = C + (size_t)(c0 + j) * p.ldc + n;
+            float o = v[j] + b;
+            if (p.accumulate) o += to_f32(*dst);
+            *dst = from_f32<TC>(o);
+          }
+        }
+      }
+      if (p.splits > 1) {
+        // the block that arrives last adds the partial tiles in split order
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        if (threadIdx.x == 64) {
+          const unsigned prev = atomicAdd(&p.tickets[tile_id], 1u);
+          *last_flag = (prev == (unsigned)p.splits - 1) ? 1u : 0u;
+          if (prev == (unsigned)p.splits - 1) p.tickets[tile_id] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          if (n < p.N) {
+            const float b = p.bias ? p.bias[n] : 0.f;
+            const float* base = p.workspace + (size_t)tile_id * p.splits * (BN * BM);
+            for (int t = 0; t < p.M; ++t) {
+              float o = b;
+              for (int z = 0; z < p.splits; ++z) o += __ldcg(base + (size_t)z * (BN * BM) + (size_t)t * BM + row);
+              TC* dst = C + (size_t)t * p.ldc + n;
+              if (p.accumulate) o += to_f32(*dst);
+              *dst = from_f32<TC>(o);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Map of a row-major [rows, K] bfloat16 matrix (row stride ld elements), tiles of box_rows x 64.
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TC>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
+  auto kern = gemm_tc_kernel<BN, STAGES, SWAP, TC>;
+  const size_t smem = Smem<BN, STAGES>::BYTES;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, THREADS, smem, stream>>>(ma, mb, p);
+  return ZK_LAUNCH_STATUS();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Bytes of float32 workspace and number of tickets a swapped launch with `splits` needs.
+long long zk_gemm_tc_workspace_bytes(int M, int N, int splits) {
+  if (splits <= 1) return 0;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  return (long long)ceil_div_i(N, BM) * splits * bn * BM * 4;
+}
+int zk_gemm_tc_tickets(int N) { return ceil_div_i(N, BM); }
+
+// X [M, K], W [N, K] bfloat16, K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
+// M <= 64 runs swapped (weights on the 128-row side) with `splits` cuts of K (workspace and
+// zeroed tickets needed when splits > 1); larger M runs normal and ignores splits.
+int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
+               int out_dtype, int accumulate, int splits, float* workspace, unsigned* tickets, int* status,
+               cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < N || !status) return ZK_EINVAL;
+  if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
+  if (out_dtype != ZK_F32 && out_dtype != ZK_BF16) return ZK_EINVAL;
+  Params p{};
+  p.C = C; p.bias = bias; p.workspace = workspace; p.tickets = tickets; p.status = status;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1;
+  CUtensorMap ma, mb;
+  const bool f32 = out_dtype == ZK_F32;
+  if (M > 64) {
+    constexpr int BN = 128;
+    if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, N, K, ldw, BN)) return ZK_EINVAL;
+    dim3 grid(ceil_div_i(M, BM), ceil_div_i(N, BN), 1);
+    return f32 ? launch<BN, 6, false, float>(ma, mb, p, grid, stream) : launch<BN, 6, false, bf16>(ma, mb, p, grid, stream);
+  }
+  const int nkb = ceil_div_i(K, BK);
+  splits = splits < 1 ? 1 : (splits > nkb ? nkb : splits);
+  while (splits > 1 && ceil_div_i(nkb, splits) * (splits - 1) >= nkb) --splits;  // no empty split
+  if (splits > 1 && (!workspace || !tickets)) return ZK_EINVAL;
+  p.splits = splits;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  if (!make_map(&ma, W, N, K, ldw, BM) || !make_map(&mb, X, M, K, ldx, bn)) return ZK_EINVAL;
+  dim3 grid(ceil_div_i(N, BM), 1, splits);
+#define ZK_TC_SWAP(BNV)                                                                     \
+  return f32 ? launch<BNV, 8, true, float>(ma, mb, p, grid, stream) : launch<BNV, 8, true, bf16>(ma, mb, p, grid, stream);
+  if (bn == 16) { ZK_TC_SWAP(16) }
+  if (bn == 32) { ZK_TC_SWAP(32) }
+  ZK_TC_SWAP(64)
+#undef ZK_TC_SWAP
+}
+
+}  // extern "C"

@@ -26,7 +26,10 @@ class StepError(RuntimeError):
     position without a page)."""
 
 
-_STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's position has no cache page"}
+_STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's position has no cache page",
+                11: "a tensor-core contraction gave up waiting for a free pipeline stage",
+                12: "a tensor-core contraction gave up waiting for its operand tiles",
+                13: "a tensor-core contraction gave up waiting for its accumulator"}
 
 
 class _DecodeGraph:
@@ -65,7 +68,7 @@ class Engine:
                                   self.dtype, self.device)
         self.calls = [CallContext(c, call.layer, self.cache.kv_view(c), self.cache.writes_kv(c),
                                   self.cache.state_view(c)) for c, call in enumerate(model.schedule)]
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = kernels.status_word(self.device)      # one status word per device, shared by all kernels
         self.vocab_size = cfg.vocab_size
         self.use_graphs = bool(use_graphs)
         self._graphs: dict[tuple, _DecodeGraph] = {}
@@ -198,13 +201,13 @@ class Engine:
         ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max_kv,
                           self.attn_split_keys, tiles=entry.tiles)
         if entry.graph is None and not entry.warmed:
-            logits = self.model.forward(ctx, self.calls, entry.want_rows)
+            logits = self.model.forward(ctx, self.calls, None, want_all=True)
             entry.warmed = True
         else:
             if entry.graph is None:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, pool=self._graph_pool):
-                    entry.logits = self.model.forward(ctx, self.calls, entry.want_rows)
+                    entry.logits = self.model.forward(ctx, self.calls, None, want_all=True)
                 entry.graph = g
             entry.graph.replay()
             logits = entry.logits

@@ -32,8 +32,16 @@ _SIGNATURES = {
         "zk_gemm_simt": "ppppiiiiiiiiip",
     },
     "gemm_skinny": {
-        "zk_gemm_skinny": "ppppiiiiiiiip",
+        "zk_gemm_skinny": "pppfpppiiiiiiiip",
+        "zk_gemm_skinny_swiglu": "pppfppiiiiiip",
+        "zk_gemm_skinny_conv": "pppfppppppp" + "iiiiiiilp",
         "zk_gemm_skinny_max_m": "",
+        "zk_gemm_skinny_fused_max_m": "",
+    },
+    "gemm_tc": {
+        "zk_gemm_tc": "ppppiiiiiiiiipppp",
+        "zk_gemm_tc_workspace_bytes": "iii",
+        "zk_gemm_tc_tickets": "i",
     },
     "shortconv": {
         "zk_conv_forward": "ppppppppiiilip",
@@ -59,6 +67,9 @@ _SIGNATURES = {
 }
 
 
+_RESTYPES = {"zk_gemm_tc_workspace_bytes": ctypes.c_longlong}
+
+
 class KernelError(RuntimeError):
     """A kernel refused its arguments or CUDA reported a failure."""
 
@@ -73,7 +84,7 @@ def _fn(lib_name: str, fn_name: str):
         for name, sig in _SIGNATURES[lib_name].items():
             g = getattr(lib, name)
             g.argtypes = [_C[c] for c in sig]
-            g.restype = ctypes.c_int
+            g.restype = _RESTYPES.get(name, ctypes.c_int)
             _funcs[name] = g
         f = _funcs[fn_name]
     return f
@@ -208,38 +219,176 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
-def gemm_skinny_max_m() -> int:
-    return _fn("gemm_skinny", "zk_gemm_skinny_max_m")()
+_device_state: dict = {}
 
 
-def gemm_skinny_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether `gemm_skinny` takes this contraction: bfloat16, few rows, 16-byte aligned rows."""
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
-            and a.shape[0] <= gemm_skinny_max_m() and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
-            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+def status_word(device) -> torch.Tensor:
+    """The int32 status word of a device: kernels that can detect a fault of their inputs or give
+    up a bounded wait write a code here; `Engine.check_status` reads and clears it."""
+    dev = torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    st = _device_state.setdefault(dev, {})
+    if "status" not in st:
+        st["status"] = torch.zeros(1, dtype=torch.int32, device=dev)
+        st["tickets"] = torch.zeros(4096, dtype=torch.int32, device=dev)
+    return st["status"]
 
 
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
-                accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out (+)= a @ w.T (+ bias) for a [M <= 64, K] on the tensor cores, every weight read once."""
-    _need(a, "a", torch.bfloat16, (None, None))
-    _need(w, "w", torch.bfloat16, (None, a.shape[1]))
-    if not gemm_skinny_takes(a, w):
-        raise KernelError(f"gemm_skinny: a {tuple(a.shape)} / w {tuple(w.shape)} need M <= {gemm_skinny_max_m()}, "
-                          "K a multiple of 8 and 16-byte aligned rows")
+def _tickets(device) -> torch.Tensor:
+    status_word(device)
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    return _device_state[dev]["tickets"]
+
+
+def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
+    """Whether the tcgen05 kernel takes this contraction: bfloat16, K a multiple of 8, rows and
+    output 16-byte aligned."""
+    ok = (isinstance(a, torch.Tensor) and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2
+          and w.dim() == 2 and a.shape[1] == w.shape[1] and a.shape[1] % 8 == 0 and a.stride(1) == 1
+          and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+          and w.data_ptr() % 16 == 0 and w.shape[0] <= 4096 * 128)
+    if ok and out is not None:
+        ok = out.stride(1) == 1 and out.data_ptr() % 16 == 0
+    return ok
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+            accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
+    More than 64 rows: 128 x 128 tiles of tokens x weight rows.  Up to 64 rows: the weights take
+    the 128-row side and K is cut into `splits` parts that are added in order."""
+    if not gemm_tc_takes(a, w, out):
+        raise KernelError(f"gemm_tc: a {tuple(a.shape)} / w {tuple(w.shape)} need bfloat16, K a multiple of 8 and "
+                          "16-byte aligned rows")
     M, K = a.shape
     N = w.shape[0]
     if out is None:
         if accumulate:
             raise KernelError("gemm: accumulate needs an output tensor")
-        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
     _need(out, "out", (torch.float32, torch.bfloat16), (M, N))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
-    _check(_fn("gemm_skinny", "zk_gemm_skinny")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0),
+    ws = None
+    if M <= 64 and splits > 1:
+        nbytes = _fn("gemm_tc", "zk_gemm_tc_workspace_bytes")(M, N, splits)
+        ws = torch.empty(nbytes // 4, dtype=torch.float32, device=a.device)
+    _check(_fn("gemm_tc", "zk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0), w.stride(0),
+                                        out.stride(0), dtype_code(out.dtype), 1 if accumulate else 0, splits,
+                                        _ptr(ws), _ptr(_tickets(a.device)), _ptr(status_word(a.device)), _stream()),
+           "gemm_tc")
+    return out
+
+
+def gemm_skinny_max_m() -> int:
+    return _fn("gemm_skinny", "zk_gemm_skinny_max_m")()
+
+
+def gemm_skinny_fused_max_m() -> int:
+    """Most rows for which the skinny kernels fuse RMSNorm, SwiGLU or the short convolution."""
+    return _fn("gemm_skinny", "zk_gemm_skinny_fused_max_m")()
+
+
+class NormInput:
+    """Rows of the float32 residual stream with an RMSNorm still to be applied: x [M, K], weight
+    [K], eps.  The skinny kernels take it in place of a bfloat16 input and normalise themselves."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float):
+        _need(x, "x", torch.float32, (None, None))
+        _need(weight, "norm weight", torch.float32, (x.shape[1],))
+        self.x, self.weight, self.eps = x, weight, float(eps)
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
+def _skinny_input(a):
+    """(X pointer, Xf pointer, norm weight pointer, eps, M, K, ldx) of a bfloat16 tensor or a NormInput."""
+    if isinstance(a, NormInput):
+        return None, _ptr(a.x), _ptr(a.weight), a.eps, a.x.shape[0], a.x.shape[1], a.x.stride(0)
+    return _ptr(a), None, None, 0.0, a.shape[0], a.shape[1], a.stride(0)
+
+
+def gemm_skinny_takes(a, w: torch.Tensor) -> bool:
+    """Whether the skinny kernels take this contraction: bfloat16 weights, few rows, 16-byte
+    aligned rows.  `a` is a bfloat16 tensor [M <= 64, K] or a NormInput [M <= 16, K]."""
+    if not (w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0):
+        return False
+    if isinstance(a, NormInput):
+        x = a.x
+        return (x.shape[0] <= gemm_skinny_fused_max_m() and x.shape[1] == w.shape[1] and x.stride(1) == 1
+                and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and a.weight.data_ptr() % 16 == 0)
+    return (a.dtype == torch.bfloat16 and a.dim() == 2 and a.shape[0] <= gemm_skinny_max_m()
+            and a.shape[1] == w.shape[1] and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0)
+
+
+def gemm_skinny_fused_takes(a, w: torch.Tensor) -> bool:
+    """Whether the fused SwiGLU / short-convolution variants take this input (at most 16 rows)."""
+    return gemm_skinny_takes(a, w) and a.shape[0] <= gemm_skinny_fused_max_m()
+
+
+def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+                accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias) for a [M <= 64, K] on the tensor cores, every weight read once.
+    With a NormInput the RMSNorm of the rows is applied inside the kernel."""
+    if not gemm_skinny_takes(a, w):
+        raise KernelError(f"gemm_skinny: a {tuple(a.shape)} / w {tuple(w.shape)} need few rows, "
+                          "K a multiple of 8 and 16-byte aligned rows")
+    X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
+    N = w.shape[0]
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=w.device)
+    _need(out, "out", (torch.float32, torch.bfloat16), (M, N))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (N,))
+    _check(_fn("gemm_skinny", "zk_gemm_skinny")(X, Xf, nw, eps, _ptr(w), _ptr(out), _ptr(bias), M, N, K, ldx,
                                                 w.stride(0), out.stride(0), dtype_code(out.dtype),
                                                 1 if accumulate else 0, _stream()), "gemm_skinny")
     return out
+
+
+def gemm_skinny_swiglu(a, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """h = silu(a W_gate^T) * (a W_up^T) in one kernel; w_gate_up [2F, K] = gate rows, then up rows."""
+    if not gemm_skinny_fused_takes(a, w_gate_up) or w_gate_up.shape[0] % 2:
+        raise KernelError("gemm_skinny_swiglu: at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
+    F = w_gate_up.shape[0] // 2
+    h = torch.empty((M, F), dtype=torch.bfloat16, device=w_gate_up.device)
+    _check(_fn("gemm_skinny", "zk_gemm_skinny_swiglu")(X, Xf, nw, eps, _ptr(w_gate_up), _ptr(h), M, F, K, ldx,
+                                                       w_gate_up.stride(0), h.stride(0), _stream()),
+           "gemm_skinny_swiglu")
+    return h
+
+
+def gemm_skinny_conv(a, w_in: torch.Tensor, in_bias, state: torch.Tensor, taps: torch.Tensor, conv_bias,
+                     seq_slot: torch.Tensor) -> torch.Tensor:
+    """Single-token step of the gated short convolution fused with its in_proj: row m of `a` is
+    sequence m; `state` [slots, K-1, D] is shifted by one; returns y [M, D]."""
+    if not gemm_skinny_fused_takes(a, w_in) or w_in.shape[0] % 3:
+        raise KernelError("gemm_skinny_conv: at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
+    D = w_in.shape[0] // 3
+    _need(taps, "conv weight", torch.float32, (None, D))
+    n_taps = taps.shape[0]
+    _need(state, "conv state", torch.float32, (None, n_taps - 1, D))
+    _need(seq_slot, "seq_slot", torch.int32, (M,))
+    if in_bias is not None:
+        _need(in_bias, "in_proj bias", torch.float32, (3 * D,))
+    if conv_bias is not None:
+        _need(conv_bias, "conv bias", torch.float32, (D,))
+    y = torch.empty((M, D), dtype=torch.bfloat16, device=w_in.device)
+    _check(_fn("gemm_skinny", "zk_gemm_skinny_conv")(X, Xf, nw, eps, _ptr(w_in), _ptr(in_bias), _ptr(state), _ptr(taps),
+                                                     _ptr(conv_bias), _ptr(seq_slot), _ptr(y), M, D, K, n_taps, ldx,
+                                                     w_in.stride(0), y.stride(0), state.stride(0), _stream()),
+           "gemm_skinny_conv")
+    return y
 
 
 # ------------------------------------------------------------------------------- short convolution

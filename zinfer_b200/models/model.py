@@ -75,13 +75,16 @@ class Model:
         return specs
 
     # ------------------------------------------------------------------ forward
-    def forward(self, ctx, calls, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    def forward(self, ctx, calls, want_rows: Optional[torch.Tensor], want_all: bool = False) -> Optional[torch.Tensor]:
         """Runs the step's tokens through every schedule entry; returns float32 logits of the rows
-        listed in `want_rows` (row indices into the packed tokens), or None when none is wanted.
-        Only wanted rows meet the final norm and the head (src/model.zig:2482-2490)."""
+        listed in `want_rows` (row indices into the packed tokens), of every row with `want_all`,
+        or None when none is wanted.  Only wanted rows meet the final norm and the head
+        (src/model.zig:2482-2490)."""
         x = self.embedding.forward(ctx, ctx.tokens)
         for call_ctx in calls:
             self.layers[call_ctx.layer].forward(ctx, call_ctx, x)
+        if want_all:
+            return self.head.forward(ctx, self.final_norm.forward(ctx, x, lazy=True))
         if want_rows is None or want_rows.numel() == 0:
             return None
         xn = self.final_norm.forward(ctx, x, rows=want_rows)

@@ -66,6 +66,8 @@ class GqaAttention(Mixer):
     def kv_request(self):
         return KVRequest(self.n_kv, self.head_dim, self.window)
 
+    takes_pending_norm = True
+
     def forward(self, ctx, call, xn, out, accumulate):
         kv = call.kv
         qkv = linear(xn, self.w_qkv)

@@ -8,7 +8,7 @@ import torch
 
 from .. import kernels
 from .base import FEED_FORWARDS, FeedForward, WeightSpec
-from .linear import linear
+from .linear import fused_input, linear
 
 
 class SwiGLU(FeedForward):
@@ -26,9 +26,14 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([weights[self.gate_name], weights[self.up_name]], dim=0).contiguous()
         self.w_down = weights[self.down_name]
 
+    takes_pending_norm = True
+
     def forward(self, ctx, xn, out, accumulate):
-        gu = linear(xn, self.w_gate_up)
-        h = kernels.silu_mul(gu)
+        x = fused_input(xn, self.w_gate_up, need_fused_rows=True)
+        if x is not None:                       # few rows: gate, up and the activation in one kernel
+            h = kernels.gemm_skinny_swiglu(x, self.w_gate_up)
+        else:
+            h = kernels.silu_mul(linear(xn, self.w_gate_up))
         linear(h, self.w_down, out=out, accumulate=accumulate)
 
 

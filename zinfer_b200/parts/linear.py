@@ -4,23 +4,66 @@ The reference has one matmul driver for every weight matrix, with an `accumulate
 folds the residual add into the store (src/model.zig:903-1026, 918-920).  Here the float32 path
 always takes the CUDA-core FMA kernel (true 32-bit); the bfloat16 path takes a tensor-core
 kernel when the shape allows one and the same FMA kernel otherwise.
+
+`a` may be a `NormedRows`: rows of the residual stream whose RMSNorm is still to be applied.
+A kernel that can normalise its input itself takes it as it is; for any other kernel the norm
+runs first, once, however many contractions read it.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Union
 
 import torch
 
 from .. import kernels
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+class NormedRows:
+    """RMSNorm(x) * weight that is computed when somebody needs it as a tensor."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.x, self.weight, self.eps, self.dtype = x, weight, eps, dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = kernels.rmsnorm(self.x, self.weight, self.eps, self.dtype)
+        return self._tensor
+
+    def kernel_input(self) -> "kernels.NormInput":
+        return kernels.NormInput(self.x, self.weight, self.eps)
+
+
+def as_tensor(a: Union[torch.Tensor, NormedRows]) -> torch.Tensor:
+    return a.tensor() if isinstance(a, NormedRows) else a
+
+
+def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_rows: bool = False):
+    """What a skinny kernel should be given for `a`, or None if it does not take it: the pending
+    norm itself when the kernel can apply it, else the (materialised) bfloat16 tensor."""
+    takes = kernels.gemm_skinny_fused_takes if need_fused_rows else kernels.gemm_skinny_takes
+    if isinstance(a, NormedRows):
+        if a.dtype != torch.bfloat16:
+            return None
+        if a._tensor is None:
+            ki = a.kernel_input()
+            if takes(ki, w):
+                return ki
+        a = a.tensor()
+    return a if takes(a, w) else None
+
+
+def linear(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
            accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a [M, K] and w [N, K] in the run dtype; result [M, N] in `out_dtype` (default: run dtype),
     or added into `out` when `accumulate`."""
-    if a.dtype == torch.bfloat16:
+    if w.dtype == torch.bfloat16:
         from . import linear_bf16
         y = linear_bf16.try_linear(a, w, out, out_dtype, accumulate, bias)
         if y is not None:
             return y
-    return kernels.gemm_simt(a, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)
+    return kernels.gemm_simt(as_tensor(a), w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)

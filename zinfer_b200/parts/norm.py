@@ -8,6 +8,7 @@ import torch
 
 from .. import kernels
 from .base import NORMS, Norm, WeightSpec
+from .linear import NormedRows
 
 
 class RMSNorm(Norm):
@@ -21,7 +22,11 @@ class RMSNorm(Norm):
     def load(self, weights, dtype, device):
         self.weight = weights[self.weight_name]
 
-    def forward(self, ctx, x, rows=None):
+    def forward(self, ctx, x, rows=None, lazy=False):
+        """The normalised rows in the run dtype.  With `lazy` (and all rows wanted) a `NormedRows`
+        is returned instead, which `linear` and the fused kernels resolve."""
+        if lazy and rows is None:
+            return NormedRows(x, self.weight, self.eps, ctx.dtype)
         return kernels.rmsnorm(x, self.weight, self.eps, ctx.dtype, rows)
 
 

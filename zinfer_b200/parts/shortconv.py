@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from .base import MIXERS, Mixer, StateRequest, WeightSpec
-from .linear import linear
+from .linear import fused_input, linear
 
 
 class ShortConv(Mixer):
@@ -53,9 +53,16 @@ class ShortConv(Mixer):
     def state_request(self):
         return StateRequest((self.K - 1, self.hidden), torch.float32)
 
+    takes_pending_norm = True
+
     def forward(self, ctx, call, xn, out, accumulate):
-        bcx = linear(xn, self.w_in, bias=self.in_bias)
         state = call.state
+        x = fused_input(xn, self.w_in, need_fused_rows=True) if ctx.is_decode else None
+        if x is not None:                       # single tokens, few rows: in_proj and convolution in one kernel
+            y = kernels.gemm_skinny_conv(x, self.w_in, self.in_bias, state, self.taps, self.conv_bias, ctx.seq_slot)
+            linear(y, self.w_out, out=out, accumulate=accumulate, bias=self.out_bias)
+            return
+        bcx = linear(xn, self.w_in, bias=self.in_bias)
         if ctx.is_decode:
             y = kernels.conv_decode(bcx, state, self.taps, self.conv_bias, ctx.seq_slot)
         else:
