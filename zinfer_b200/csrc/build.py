@@ -1,8 +1,8 @@
 """Compiles the CUDA sources of this folder for sm_100a and loads them through ctypes.
 
 Each `.cu` file becomes one shared library `_build/<name>-<hash>.so`, built by nvcc the first
-time something needs it and reused afterwards; the hash covers the source, the shared headers
-and the flags, so an edited file is rebuilt.  Nothing here falls back to another
+time something needs it and reused afterwards; the hash covers every source and header of the
+folder and the flags, so an edit rebuilds what may depend on it.  Nothing here falls back to another
 implementation: a missing compiler or a failed build raises `KernelBuildError`.
 """
 from __future__ import annotations
@@ -70,7 +70,8 @@ def _build_dir() -> Path:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
-    for p in [SRC_DIR / f"{name}.cu", *sorted(SRC_DIR.glob("*.cuh"))]:
+    # every source and header of the folder: a library may include any of them
+    for p in sorted([*SRC_DIR.glob("*.cu"), *SRC_DIR.glob("*.cuh"), *SRC_DIR.glob("*.h")]):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     return h.hexdigest()[:16]
