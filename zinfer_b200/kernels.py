@@ -52,6 +52,10 @@ _SIGNATURES = {
         "zk_attn_decode": "ppppppppp" + "iiiiiiifiip",
         "zk_attn_decode_takes": "iiii",
     },
+    "attention_decode_noalloc": {      # for C callers that must not allocate; see csrc/attention_decode_noalloc.h
+        "zk_attn_decode_noalloc": "ppppppp" + "iiiiiiifiip",
+        "zk_attn_decode_noalloc_bytes": "iiii",
+    },
     "sampling": {
         "zk_apply_penalties": "piipifppip",
         "zk_argmax": "piipp",
@@ -67,7 +71,7 @@ _SIGNATURES = {
 }
 
 
-_RESTYPES = {"zk_gemm_tc_workspace_bytes": ctypes.c_longlong}
+_RESTYPES = {"zk_gemm_tc_workspace_bytes": ctypes.c_longlong, "zk_attn_decode_noalloc_bytes": ctypes.c_longlong}
 
 
 class KernelError(RuntimeError):
