@@ -341,7 +341,8 @@ class PagedSetup:
                                                        (5, 5, 48, 64, 48, False), (8, 2, 80, 16, 40, True),
                                                        (6, 2, 128, 64, 128, False), (20, 1, 64, 32, 64, False),
                                                        (32, 8, 64, 64, 64, False), (7, 7, 96, 32, 96, False),
-                                                       (16, 2, 32, 64, 32, False)])
+                                                       (16, 2, 32, 64, 32, False), (6, 2, 64, 128, 64, False),
+                                                       (5, 1, 128, 64, 64, True), (16, 1, 64, 64, 64, False)])
 def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
     """Prompt step of unequal lengths into NaN-filled shuffled pages, then a single-token step
     with and without key splits, against whole-sequence references."""
@@ -371,7 +372,7 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
             q, kk, v = q.bfloat16().double(), kk.bfloat16().double(), v.bfloat16().double()
         return q, kk, v
 
-    def run(step_lens, starts, rows, num_splits=1, split_keys=0, single_token=False):
+    def run(step_lens, starts, rows, num_splits=1, split_keys=0, single_token=False, kind=None):
         cu = np.concatenate([[0], np.cumsum(step_lens)]).astype(np.int32)
         tok_seq = torch.from_numpy(np.repeat(np.arange(len(step_lens)), step_lens).astype(np.int32)).cuda()
         tok_pos = torch.from_numpy(np.concatenate([np.arange(s, s + l) for s, l in zip(starts, step_lens)]).astype(np.int32)).cuda()
@@ -381,9 +382,11 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
         q = k.qk_prepare(rows.cuda(), setup.k, setup.v, qw, kw, inv_freq, tok_seq, tok_pos, seq_slot, setup.table_dev,
                          H, Hkv, hd, n_rot, inter, eps, status)
         bq, _ = k.attn_tile_shape(H, Hkv)
+        if kind == "prompt_tc":
+            bq = k.attention_plan(dtype, H, Hkv, hd, page, False)[1]
         tiles = torch.from_numpy(attn_tiles_host(step_lens, bq)).cuda()
         return k.attention(q, setup.k, setup.v, tiles[0].contiguous(), tiles[1].contiguous(), cu_q, seq_start,
-                           seq_slot, setup.table_dev, H, Hkv, hd, scale, 0, num_splits, split_keys, single_token)
+                           seq_slot, setup.table_dev, H, Hkv, hd, scale, 0, num_splits, split_keys, single_token, kind)
 
     out = run(lens, [0] * len(lens), torch.cat([s[:-1] for s in seqs]))
     assert status.item() == 0
@@ -392,6 +395,10 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
         q, kk, v = reference(i, l)
         ref.append(attn_ref(q, kk, v, 0, 0, scale).reshape(l, H * hd))
     close(out, torch.cat(ref), dtype, "prefill attention")
+    if k.attention_plan(dtype, H, Hkv, hd, page, False)[0] == "prompt_tc":
+        again = run(lens, [0] * len(lens), torch.cat([s[:-1] for s in seqs]), kind="prompt_tc")
+        close(again, torch.cat(ref), dtype, "prefill attention on the tensor cores")
+        assert not torch.isnan(again.float()).any()
     last = torch.stack([s[-1] for s in seqs])
     ref = []
     for i, l in enumerate(lens):

@@ -225,58 +225,64 @@ __global__ void __launch_bounds__(THREADS)
     const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
 
     if constexpr (!SWAP) {
-      const int m = a_tile * BM + row;
-      TC* crow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc;
+      // The accumulator goes through shared memory (the pipeline's stages are free by now: every
+      // MMA has read them) so that global rows are read and written as whole 128-byte lines.
+      constexpr int LD = BN + 1;  // odd row stride: a warp's 32 rows fall into 32 banks
+      float* stage = reinterpret_cast<float*>(tiles);
+      static_assert((size_t)BM * LD * 4 <= (size_t)STAGES * S::STAGE_BYTES, "tile does not fit the stages");
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
-        if (ok) tmem_ld16(lane_addr + c0, v);   // warp-collective: every lane of the warp takes part
-        const int n0 = b_tile * BN + c0;
-        if (!ok || m >= p.M || n0 >= p.N) continue;
-        if (n0 + 16 <= p.N && (p.ldc % 8) == 0) {
-          if (p.bias) {
+        if (ok) {
+          tmem_ld16(lane_addr + c0, v);   // warp-collective
+        } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += p.bias[n0 + j];
-          }
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stage[row * LD + c0 + j] = v[j];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+      if (ok) {
+        const int n_base = b_tile * BN;
+        for (int r = quarter * 32; r < quarter * 32 + 32; ++r) {
+          const int m = a_tile * BM + r;
+          if (m >= p.M) break;
+          TC* crow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc + n_base;
+          const float* srow = stage + r * LD;
           if constexpr (sizeof(TC) == 4) {
-            float4* dst = reinterpret_cast<float4*>(crow + n0);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              if (p.accumulate) {
-                const float4 old = dst[j];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            for (int i = 0; i < BN / 32; ++i) {
+              const int col = lane + 32 * i;
+              if (n_base + col < p.N) {
+                float o = srow[col] + (p.bias ? p.bias[n_base + col] : 0.f);
+                if (p.accumulate) o += crow[col];
+                crow[col] = o;
               }
-              dst[j] = o;
             }
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(crow + n0);
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              float w[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) w[i] = v[8 * j + i];
-              if (p.accumulate) {
-                const uint4 old = dst[j];
-                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  w[2 * i] += __low2float(ob[i]);
-                  w[2 * i + 1] += __high2float(ob[i]);
+            for (int i = 0; i < BN / 64; ++i) {
+              const int col = 2 * lane + 64 * i;
+              if (n_base + col + 1 < p.N && (p.ldc & 1) == 0) {
+                float o0 = srow[col] + (p.bias ? p.bias[n_base + col] : 0.f);
+                float o1 = srow[col + 1] + (p.bias ? p.bias[n_base + col + 1] : 0.f);
+                __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(crow + col);
+                if (p.accumulate) {
+                  const __nv_bfloat162 old = *dst;
+                  o0 += __low2float(old);
+                  o1 += __high2float(old);
                 }
+                *dst = __floats2bfloat162_rn(o0, o1);
+              } else {
+                for (int e = 0; e < 2; ++e)
+                  if (n_base + col + e < p.N) {
+                    float o = srow[col + e] + (p.bias ? p.bias[n_base + col + e] : 0.f);
+                    if (p.accumulate) o += to_f32(crow[col + e]);
+                    crow[col + e] = from_f32<TC>(o);
+                  }
               }
-              uint4 o;
-              __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(w[2 * i], w[2 * i + 1]);
-              dst[j] = o;
             }
-          }
-        } else {
-          for (int j = 0; j < 16 && n0 + j < p.N; ++j) {
-            float o = v[j] + (p.bias ? p.bias[n0 + j] : 0.f);
-            if (p.accumulate) o += to_f32(crow[n0 + j]);
-            crow[n0 + j] = from_f32<TC>(o);
           }
         }
       }

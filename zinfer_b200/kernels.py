@@ -56,6 +56,11 @@ _SIGNATURES = {
         "zk_attn_decode_noalloc": "ppppppp" + "iiiiiiifiip",
         "zk_attn_decode_noalloc_bytes": "iiii",
     },
+    "attention_prefill": {
+        "zk_attn_prefill": "pppppppppp" + "iiiiiiifp",
+        "zk_attn_prefill_takes": "iiii",
+        "zk_attn_prefill_tile_tokens": "ii",
+    },
     "sampling": {
         "zk_apply_penalties": "piipifppip",
         "zk_argmax": "piipp",
@@ -505,13 +510,27 @@ def attn_tile_shape(n_heads: int, n_kv: int) -> tuple[int, int]:
     return max(1, rows // gc), gc
 
 
+def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+                   single_token: bool) -> tuple[str, int]:
+    """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
+    ("single_token" | "prompt_tc" | "general", tokens per tile)."""
+    if dtype == torch.bfloat16 and n_heads % n_kv == 0:
+        if single_token and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size):
+            return "single_token", 1
+        if not single_token and _fn("attention_prefill", "zk_attn_prefill_takes")(n_heads, n_kv, head_dim, page_size):
+            return "prompt_tc", _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_kv)
+    return "general", attn_tile_shape(n_heads, n_kv)[0]
+
+
 def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, n_heads: int, n_kv: int,
               head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0,
-              single_token: bool = False) -> torch.Tensor:
+              single_token: bool = False, kind: Optional[str] = None) -> torch.Tensor:
     """Causal grouped-query attention of a packed batch against the paged cache.  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
-    bfloat16 kernel for that case is used when it takes the sizes."""
+    bfloat16 kernel for that case is used when it takes the sizes.  `kind` names the kernel as
+    `attention_plan` chose it (the tile table must then have that plan's tokens per tile);
+    without it the general kernel or the single-token kernel runs."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
     n = q.shape[0]
     for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
@@ -528,7 +547,16 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if num_splits > 1:
         part_o = torch.empty((num_splits, n * n_heads, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
-    if (single_token and q.dtype == torch.bfloat16
+    if kind == "prompt_tc":
+        if q.dtype != torch.bfloat16 or not _fn("attention_prefill", "zk_attn_prefill_takes")(n_heads, n_kv, head_dim,
+                                                                                            page_size):
+            raise KernelError("attention: the tensor-core prompt kernel does not take these sizes")
+        _check(_fn("attention_prefill", "zk_attn_prefill")(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
+            _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n_heads, n_kv, head_dim,
+            page_size, window, scale, _stream()), "attention (prompt, tensor cores)")
+        return out
+    if (single_token and kind in (None, "single_token") and q.dtype == torch.bfloat16
             and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode", "zk_attn_decode")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),

@@ -87,11 +87,13 @@ class GqaAttention(Mixer):
             self.position.apply(ctx, normed[:, :self.q_dim], normed[:, self.q_dim:self.q_dim + self.kv_dim])
             q = kernels.qk_prepare(normed, kv.k, kv.v, None, None, None, n_rot=0, interleaved=False,
                                    write_kv=call.writes_kv, **common)
-        tile_seq, tile_q0 = ctx.attn_tiles(kernels.attn_tile_shape(self.n_heads, self.n_kv)[0])
+        kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
+                                                   ctx.is_decode)
+        tile_seq, tile_q0 = ctx.attn_tiles(tile_tokens)
         num_splits, split_keys = ctx.kv_splits(self.n_kv)
         att = kernels.attention(q, kv.k, kv.v, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot,
                                 kv.page_table, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
-                                num_splits, split_keys, single_token=ctx.is_decode)
+                                num_splits, split_keys, single_token=ctx.is_decode, kind=kind)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 
