@@ -23,7 +23,6 @@
 
 namespace {
 
-constexpr int WARPS = 8;
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_CONV = 2 };
 
 struct Args {
@@ -69,7 +68,7 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 // RG: groups of 16 weight rows per block; NT: groups of 8 tokens; UNROLL: 32-wide k slabs whose
 // weight loads are in flight together.  N is the number of output columns; for EPI_PLAIN weight
 // row = column, for the fused epilogues group r holds weight rows r*N + column.
-template <int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
+template <int WARPS, int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
 __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   extern __shared__ float smem[];
   constexpr int RED_LD = NT * 8 + 1;
@@ -111,7 +110,11 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
         for (int h = 0; h < 2; ++h) wv[u][r][h] = (kok && wok[r][h]) ? ld16_stream(wrow[r][h] + k) : zero;
     }
   };
-  load_w(s_begin);  // the first weights are under way while the norm is computed
+  // Loads of the next slabs are issued after the MMAs of the current ones when a slab carries
+  // much arithmetic (many tokens) or a norm prologue can hide them, else at the top of the loop;
+  // measured, not derived.
+  constexpr bool PIPE = NT >= 4 || NORM;
+  if (PIPE) load_w(s_begin);
 
   // NORM: the block normalises the M rows once into shared memory as bfloat16 (row stride padded
   // by 16 bytes so that the 8 rows a fragment load touches fall into different banks).
@@ -175,6 +178,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   for (int t = 0; t < NT; ++t) xok[t] = t * 8 + g < M;
 
   for (int s = s_begin; s < s_end; s += UNROLL) {
+    if (!PIPE) load_w(s);
     uint4 xv[UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -200,7 +204,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
           mma16816(acc[r][t], wv[u][r][0].x, wv[u][r][1].x, wv[u][r][0].y, wv[u][r][1].y, xv[u][t].x, xv[u][t].y);
           mma16816(acc[r][t], wv[u][r][0].z, wv[u][r][1].z, wv[u][r][0].w, wv[u][r][1].w, xv[u][t].z, xv[u][t].w);
         }
-    if (s + UNROLL < s_end) load_w(s + UNROLL);
+    if (PIPE && s + UNROLL < s_end) load_w(s + UNROLL);
   }
 
   // partial sums of the 8 warps -> shared memory; C fragment: rows g, g+8; columns 2c, 2c+1
@@ -273,17 +277,17 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   }
 }
 
-template <int RG, int NT>
+template <int WARPS, int RG, int NT>
 size_t smem_bytes(bool norm, int K) {
   size_t floats = (size_t)WARPS * RG * 16 * (NT * 8 + 1) + NT * 8 + NT * 8 * WARPS;
   floats = (floats + 3) / 4 * 4;  // the bfloat16 rows start 16-byte aligned
   return sizeof(float) * floats + (norm ? sizeof(bf16) * (size_t)NT * 8 * (K + 8) : 0);
 }
 
-template <int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
+template <int WARPS, int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
 int launch(const Args& a, cudaStream_t stream) {
-  auto kern = skinny_kernel<RG, NT, UNROLL, EPI, NORM, TC>;
-  const size_t smem = smem_bytes<RG, NT>(NORM, a.K);
+  auto kern = skinny_kernel<WARPS, RG, NT, UNROLL, EPI, NORM, TC>;
+  const size_t smem = smem_bytes<WARPS, RG, NT>(NORM, a.K);
   if (smem > 200 * 1024) return ZK_EINVAL;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -294,24 +298,38 @@ int launch(const Args& a, cudaStream_t stream) {
   return ZK_LAUNCH_STATUS();
 }
 
+// Shapes are chosen so that a block streams enough weights to pay for its start-up and so that an
+// SM has some 64 KB of loads in flight: 16 warps where N gives few blocks, 32 rows per block
+// where N gives many.
 template <bool NORM, typename TC>
 int dispatch_plain(const Args& a, cudaStream_t stream) {
-  const bool wide = a.N >= 16 * 148 * 8;  // 32 rows per block once 16 would give every SM many blocks
-  if (a.M <= 8) return wide ? launch<2, 1, 4, EPI_PLAIN, NORM, TC>(a, stream) : launch<1, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
-  if (a.M <= 16) return wide ? launch<2, 2, 4, EPI_PLAIN, NORM, TC>(a, stream) : launch<1, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
+  const bool few = a.N <= 16 * 148 * 2;    // at most two 16-row blocks per SM: make each block wider in K
+  const bool many = a.N >= 16 * 148 * 6;   // many blocks: 32 rows each
+  if (a.M <= 8) {
+    if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
+    if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
+    return launch<8, 1, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
+  }
+  if (a.M <= 16) {
+    if (few) return launch<16, 1, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
+    if (many) return launch<8, 2, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
+    return launch<8, 1, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
+  }
   if constexpr (NORM) {
     return ZK_EINVAL;
   } else {
-    if (a.M <= 32) return launch<2, 4, 2, EPI_PLAIN, false, TC>(a, stream);
-    return launch<1, 8, 2, EPI_PLAIN, false, TC>(a, stream);
+    // the split of K over the warps must not depend on M, or a row's bits would depend on its batch
+    if (a.M <= 32) return few ? launch<16, 1, 4, 2, EPI_PLAIN, false, TC>(a, stream)
+                              : launch<8, 2, 4, 2, EPI_PLAIN, false, TC>(a, stream);
+    return few ? launch<16, 1, 8, 1, EPI_PLAIN, false, TC>(a, stream) : launch<8, 1, 8, 2, EPI_PLAIN, false, TC>(a, stream);
   }
 }
 
 template <int RG, int EPI>
 int dispatch_fused(const Args& a, cudaStream_t stream) {
   const bool norm = a.Xf != nullptr;
-  if (a.M <= 8) return norm ? launch<RG, 1, 4, EPI, true, bf16>(a, stream) : launch<RG, 1, 4, EPI, false, bf16>(a, stream);
-  if (a.M <= 16) return norm ? launch<RG, 2, 2, EPI, true, bf16>(a, stream) : launch<RG, 2, 2, EPI, false, bf16>(a, stream);
+  if (a.M <= 8) return norm ? launch<8, RG, 1, 4, EPI, true, bf16>(a, stream) : launch<8, RG, 1, 4, EPI, false, bf16>(a, stream);
+  if (a.M <= 16) return norm ? launch<8, RG, 2, 2, EPI, true, bf16>(a, stream) : launch<8, RG, 2, 2, EPI, false, bf16>(a, stream);
   return ZK_EINVAL;
 }
 

@@ -429,7 +429,7 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   if (!make_map(&ma, W, N, K, ldw, BM) || !make_map(&mb, X, M, K, ldx, bn)) return ZK_EINVAL;
   dim3 grid(ceil_div_i(N, BM), 1, splits);
 #define ZK_TC_SWAP(BNV)                                                                     \
-  return f32 ? launch<BNV, 8, true, float>(ma, mb, p, grid, stream) : launch<BNV, 8, true, bf16>(ma, mb, p, grid, stream);
+  return f32 ? launch<BNV, 4, true, float>(ma, mb, p, grid, stream) : launch<BNV, 4, true, bf16>(ma, mb, p, grid, stream);
   if (bn == 16) { ZK_TC_SWAP(16) }
   if (bn == 32) { ZK_TC_SWAP(32) }
   ZK_TC_SWAP(64)

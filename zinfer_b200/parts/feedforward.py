@@ -11,6 +11,9 @@ from .base import FEED_FORWARDS, FeedForward, WeightSpec
 from .linear import fused_input, linear
 
 
+FUSED_SWIGLU_MAX_ROWS = 2
+
+
 class SwiGLU(FeedForward):
     def __init__(self, hidden: int, ffn_dim: int, gate_name: str, up_name: str, down_name: str):
         self.hidden, self.ffn_dim = hidden, ffn_dim
@@ -29,8 +32,12 @@ class SwiGLU(FeedForward):
     takes_pending_norm = True
 
     def forward(self, ctx, xn, out, accumulate):
-        x = fused_input(xn, self.w_gate_up, need_fused_rows=True)
-        if x is not None:                       # few rows: gate, up and the activation in one kernel
+        # One kernel for gate, up and the activation pays only for one or two rows: its two row
+        # groups lie F rows apart in memory and stream slower than 32 adjacent rows (measured at 8
+        # rows: 19.1 us fused against 13.7 + 3 us for the plain contraction and the activation).
+        x = fused_input(xn, self.w_gate_up, need_fused_rows=True, blocks=-(-self.ffn_dim // 16)) \
+            if xn.shape[0] <= FUSED_SWIGLU_MAX_ROWS else None
+        if x is not None:
             h = kernels.gemm_skinny_swiglu(x, self.w_gate_up)
         else:
             h = kernels.silu_mul(linear(xn, self.w_gate_up))

@@ -42,16 +42,28 @@ def as_tensor(a: Union[torch.Tensor, NormedRows]) -> torch.Tensor:
     return a.tensor() if isinstance(a, NormedRows) else a
 
 
-def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_rows: bool = False):
+# A block that applies the norm itself reads all M rows again, so fusing the norm pays only while
+# few blocks do so (about one per SM) or the rows are very few; measured on the LFM2-1.2B shapes:
+# fused 12.5 us against 14.5 us for the short convolution's in_proj (128 blocks, 8 rows), but
+# 75 us against 50 us for the head (2048 blocks).
+NORM_FUSION_MAX_BLOCKS = 160
+NORM_FUSION_ANY_BLOCKS_ROWS = 2
+
+
+def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_rows: bool = False,
+                blocks: Optional[int] = None):
     """What a skinny kernel should be given for `a`, or None if it does not take it: the pending
-    norm itself when the kernel can apply it, else the (materialised) bfloat16 tensor."""
+    norm itself when the kernel can apply it and that is the faster way (`blocks` = thread blocks
+    the kernel will run, default one per 16 weight rows), else the (materialised) bfloat16 tensor."""
     takes = kernels.gemm_skinny_fused_takes if need_fused_rows else kernels.gemm_skinny_takes
     if isinstance(a, NormedRows):
         if a.dtype != torch.bfloat16:
             return None
         if a._tensor is None:
             ki = a.kernel_input()
-            if takes(ki, w):
+            n_blocks = blocks if blocks is not None else -(-w.shape[0] // 16)
+            worth = n_blocks <= NORM_FUSION_MAX_BLOCKS or a.shape[0] <= NORM_FUSION_ANY_BLOCKS_ROWS
+            if worth and takes(ki, w):
                 return ki
         a = a.tensor()
     return a if takes(a, w) else None

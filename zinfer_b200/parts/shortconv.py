@@ -57,7 +57,7 @@ class ShortConv(Mixer):
 
     def forward(self, ctx, call, xn, out, accumulate):
         state = call.state
-        x = fused_input(xn, self.w_in, need_fused_rows=True) if ctx.is_decode else None
+        x = fused_input(xn, self.w_in, need_fused_rows=True, blocks=-(-self.hidden // 16)) if ctx.is_decode else None
         if x is not None:                       # single tokens, few rows: in_proj and convolution in one kernel
             y = kernels.gemm_skinny_conv(x, self.w_in, self.in_bias, state, self.taps, self.conv_bias, ctx.seq_slot)
             linear(y, self.w_out, out=out, accumulate=accumulate, bias=self.out_bias)
