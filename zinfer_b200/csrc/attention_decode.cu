@@ -88,15 +88,34 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
     const size_t row0 = (((size_t)page * Hkv + kvh) * page_size + base % page_size) * HD;
     const bool valid = lane >= j_lo && lane < j_hi;
 
+    // The tile's K row of this lane and, for head sizes up to 64, all of its V rows are requested
+    // before any arithmetic: a warp has few tiles, so what it waits for must be in flight at once.
+    constexpr bool PREFETCH_V = VPL <= 2;
+    uint4 kv[HD / 8];
+    if (valid) {
+      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + row0 + (size_t)lane * HD);
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) kv[c] = kr[c];
+    }
+    const bf16* vr = v_cache + row0 + (size_t)lane * VPL;
+    float vpre[PREFETCH_V ? DEC_TK : 1][VPL];
+    if constexpr (PREFETCH_V) {
+#pragma unroll
+      for (int j = 0; j < DEC_TK; ++j) {
+        if (j >= j_lo && j < j_hi) {
+          load_v<VPL>(vr + (size_t)j * HD, vpre[j]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VPL; ++i) vpre[j][i] = 0.f;
+        }
+      }
+    }
+
     // scores: this lane's key against the G query heads
     float s[G];
 #pragma unroll
     for (int h = 0; h < G; ++h) s[h] = 0.f;
     if (valid) {
-      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + row0 + (size_t)lane * HD);
-      uint4 kv[HD / 8];
-#pragma unroll
-      for (int c = 0; c < HD / 8; ++c) kv[c] = kr[c];
 #pragma unroll
       for (int c = 0; c < HD / 8; ++c) {
         float kf[8];
@@ -129,11 +148,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
       for (int i = 0; i < VPL; ++i) o[h][i] *= alpha;
     }
     // P.V: V rows of the tile, read coalesced; this lane owns columns lane*VPL .. lane*VPL+VPL-1
-    const bf16* vr = v_cache + row0 + (size_t)lane * VPL;
-#pragma unroll 8
+#pragma unroll
     for (int j = 0; j < DEC_TK; ++j) {
       float v[VPL];
-      if (j >= j_lo && j < j_hi) {
+      if constexpr (PREFETCH_V) {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) v[i] = vpre[j][i];
+      } else if (j >= j_lo && j < j_hi) {
         load_v<VPL>(vr + (size_t)j * HD, v);
       } else {
 #pragma unroll

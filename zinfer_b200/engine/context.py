@@ -112,10 +112,10 @@ class StepContext:
         if not self.is_decode or self.max_kv_len <= 0:
             return 1, 0
         keys = self._split_keys
-        if keys <= 0:
+        if keys <= 0:                     # about four blocks per SM, chunks of at least 128 keys
             blocks = max(1, self.n_seqs * n_kv_heads)
-            want = max(1, -(-296 // blocks))
-            keys = max(256, -(-self.max_kv_len // want))
-            keys = -(-keys // 256) * 256
+            want = max(1, -(-592 // blocks))
+            keys = max(128, -(-self.max_kv_len // want))
+            keys = -(-keys // 64) * 64
         n = -(-self.max_kv_len // keys)
         return (n, keys) if n > 1 else (1, 0)
