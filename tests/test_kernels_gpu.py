@@ -66,12 +66,20 @@ def test_rmsnorm(k, dtype, n, dim, eps):
     close(k.rmsnorm(x, w, eps, dtype, rows), ref[[n - 1, 0]], dtype, "rmsnorm rows")
 
 
+def interleaved(parts, group=16):
+    from zinfer_b200.parts.linear import interleave_rows
+    return interleave_rows(parts, group)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(k, dtype):
-    n, F = 7, 200
+    n, F = 7, 208
     gu = rnd((n, 2 * F), 4, dtype, 2.0).cuda()
     g, u = gu[:, :F].double(), gu[:, F:].double()
-    close(k.silu_mul(gu), g / (1 + torch.exp(-g)) * u, dtype, "silu_mul")
+    ref = g / (1 + torch.exp(-g)) * u
+    close(k.silu_mul(gu), ref, dtype, "silu_mul")
+    mixed = interleaved([gu[:, :F].T.contiguous(), gu[:, F:].T.contiguous()]).T.contiguous()
+    close(k.silu_mul(mixed, interleave=16), ref, dtype, "silu_mul, groups of 16")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -164,9 +172,11 @@ def test_gemm_skinny_with_fused_norm(k, M, N, K):
     assert not k.gemm_skinny_takes(k.NormInput(rnd((17, K), 1, torch.float32).cuda(), nw, 1e-5), w)
 
 
-@pytest.mark.parametrize("M,F,K,norm", [(1, 200, 80, False), (8, 8192, 2048, True), (16, 136, 96, True), (5, 17, 64, False)])
+@pytest.mark.parametrize("M,F,K,norm", [(1, 208, 80, False), (8, 8192, 2048, True), (16, 144, 96, True), (5, 32, 64, False)])
 def test_gemm_skinny_swiglu(k, M, F, K, norm):
-    w = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
+    halves = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
+    w_mixed = interleaved([halves[:F], halves[F:]])
+    w = halves
     if norm:
         x = rnd((M, K), 1, torch.float32, 2.0).cuda()
         nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
@@ -175,13 +185,27 @@ def test_gemm_skinny_swiglu(k, M, F, K, norm):
         inp = rnd((M, K), 1, torch.bfloat16).cuda()
         a = inp.double()
     g, u = a @ w[:F].double().T, a @ w[F:].double().T
-    close(k.gemm_skinny_swiglu(inp, w), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "skinny swiglu")
+    close(k.gemm_skinny_swiglu(inp, w_mixed), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "skinny swiglu")
+    with pytest.raises(k.KernelError):
+        k.gemm_skinny_swiglu(inp, w_mixed[:48])        # 24 outputs: not whole groups of 16
+
+
+@pytest.mark.parametrize("M,F,K", [(65, 64, 64), (300, 8192, 2048), (130, 208, 520)])
+def test_gemm_tc_with_swiglu_epilogue(k, M, F, K):
+    a = rnd((M, K), 1, torch.bfloat16).cuda()
+    halves = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
+    g, u = a.double() @ halves[:F].double().T, a.double() @ halves[F:].double().T
+    h = k.gemm_tc(a, interleaved([halves[:F], halves[F:]]), swiglu=True)
+    assert h.shape == (M, F)
+    close(h, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "tcgen05 contraction with SwiGLU epilogue")
+    assert k.status_word("cuda").item() == 0
 
 
 @pytest.mark.parametrize("M,D,K,taps,bias,norm", [(1, 80, 80, 2, False, False), (8, 2048, 2048, 3, False, True),
-                                                  (13, 96, 96, 4, True, True), (16, 40, 64, 7, True, False)])
+                                                  (13, 96, 96, 4, True, True), (16, 48, 64, 7, True, False)])
 def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
-    """Three fused single-token steps against in_proj + conv_decode, state included."""
+    """Three fused single-token steps against in_proj + conv_decode, state included; in_proj's rows
+    are stored as groups of 16 B, 16 C, 16 X rows for both paths."""
     w_in = rnd((3 * D, K), 3, torch.bfloat16, 0.2).cuda()
     tw = rnd((taps, D), 4, torch.float32).cuda()
     in_b = rnd((3 * D,), 5, torch.float32).cuda() if bias else None
@@ -198,7 +222,7 @@ def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
             inp = xn = x.bfloat16()
         y_fused = k.gemm_skinny_conv(inp, w_in, in_b, st_a, tw, cb, slots)
         bcx = k.gemm_skinny(xn, w_in, bias=in_b)
-        y_ref = k.conv_decode(bcx, st_b, tw, cb, slots)
+        y_ref = k.conv_decode(bcx, st_b, tw, cb, slots, interleave=16)
         close(y_fused, y_ref.double(), torch.bfloat16, f"fused conv step {step}")
         close(st_a, st_b.double(), torch.bfloat16, f"fused conv state {step}")
     untouched = [i for i in range(M + 3) if i not in slots.cpu().tolist()]
@@ -252,7 +276,15 @@ def test_short_conv_packed_and_stepwise(k, dtype, D, K, use_bias):
     seq_slot = torch.tensor(slots, dtype=torch.int32).cuda()
     bcx = torch.cat(seqs).cuda()
     y = k.conv_forward(bcx, state, taps, bias, tok_seq, cu_q, seq_slot)
+    if D % 16 == 0:      # the same step with the columns stored as groups of 16 B, 16 C, 16 X
+        mixed = interleaved([bcx[:, :D].T.contiguous(), bcx[:, D:2 * D].T.contiguous(), bcx[:, 2 * D:].T.contiguous()]).T.contiguous()
+        y_mixed = k.conv_forward(mixed, state, taps, bias, tok_seq, cu_q, seq_slot, interleave=16)
+        assert torch.equal(y_mixed, y)
+        state_mixed = state.clone()
+        k.conv_state_update(mixed, state_mixed, cu_q, seq_slot, len(lens), K, interleave=16)
     k.conv_state_update(bcx, state, cu_q, seq_slot, len(lens), K)
+    if D % 16 == 0:
+        assert torch.equal(state_mixed, state)
     refs = [conv_ref(s.double(), taps.double().cpu(), None if bias is None else bias.double().cpu(),
                      torch.zeros(K - 1, D, dtype=torch.float64)) for s in seqs]
     close(y, torch.cat([r[0] for r in refs]), dtype, "conv prefill y")

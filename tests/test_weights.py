@@ -44,7 +44,12 @@ def test_loads_by_name_with_kept_dtypes(folder_b):
     got = load_model(folder_b, dtype=torch.float32, device="cpu")
     assert np.array_equal(got.layers[1].mixer.taps.numpy(), plain["model.layers.1.conv.conv.weight"].reshape(96, 4).T)
     assert np.array_equal(got.layers[0].mixer.w_qkv[:96].numpy(), plain["model.layers.0.self_attn.q_proj.weight"])
-    assert np.array_equal(got.layers[0].ffn.w_gate_up[192:].numpy(), plain["model.layers.0.feed_forward.w3.weight"])
+    # gate and up are stacked in groups of 16 rows: 16 of w1, the same 16 of w3, ...
+    gu = got.layers[0].ffn.w_gate_up.numpy().reshape(12, 2, 16, 96)
+    assert np.array_equal(gu[:, 0].reshape(192, 96), plain["model.layers.0.feed_forward.w1.weight"])
+    assert np.array_equal(gu[:, 1].reshape(192, 96), plain["model.layers.0.feed_forward.w3.weight"])
+    bcx = got.layers[1].mixer.w_in.numpy().reshape(6, 3, 16, 96)
+    assert np.array_equal(bcx[:, 2].reshape(96, 96), plain["model.layers.1.conv.in_proj.weight"][192:])
 
 
 def test_tied_head_uses_the_embedding(tmp_path):

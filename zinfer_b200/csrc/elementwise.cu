@@ -35,15 +35,18 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   for (int d = threadIdx.x; d < dim; d += blockDim.x) yr[d] = from_f32<TO>((xr[d] * scale) * w[d]);
 }
 
-// h[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(g) = g / (1 + exp(-g))
-// (src/ffn.zig:31-33, 49-57).
+// h[t, f] = silu(gate_f) * up_f, silu(g) = g / (1 + exp(-g)) (src/ffn.zig:31-33, 49-57).
+// A row of gu holds [gate (F) | up (F)] (il = 0), or groups of il gates followed by their il ups
+// (il > 0, the layout the fused contraction kernels want).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int n, int F) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int n, int F, int il) {
   const size_t total = (size_t)n * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / F, f = i - t * F;
-    const float g = to_f32(gu[t * 2 * F + f]);
-    const float u = to_f32(gu[t * 2 * F + F + f]);
+    const size_t gi = il ? (f / il) * 2 * il + f % il : f;
+    const size_t ui = il ? gi + il : F + f;
+    const float g = to_f32(gu[t * 2 * F + gi]);
+    const float u = to_f32(gu[t * 2 * F + ui]);
     h[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
   }
 }
@@ -118,16 +121,16 @@ int zk_rmsnorm(const float* x, const int* rows, const float* w, void* y, int n_o
   return ZK_LAUNCH_STATUS();
 }
 
-int zk_silu_mul(const void* gu, void* h, int n, int F, int dtype, cudaStream_t stream) {
+int zk_silu_mul(const void* gu, void* h, int n, int F, int il, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (F <= 0) return ZK_EINVAL;
+  if (F <= 0 || il < 0 || (il > 0 && F % il)) return ZK_EINVAL;
   const size_t total = (size_t)n * F;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == ZK_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)h, n, F);
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)h, n, F, il);
   else if (dtype == ZK_BF16)
-    silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)h, n, F);
+    silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)h, n, F, il);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();

@@ -67,7 +67,7 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 
 // RG: groups of 16 weight rows per block; NT: groups of 8 tokens; UNROLL: 32-wide k slabs whose
 // weight loads are in flight together.  N is the number of output columns; for EPI_PLAIN weight
-// row = column, for the fused epilogues group r holds weight rows r*N + column.
+// row = column, for the fused epilogues block b holds weight rows b*16*RG .. (interleaved parts).
 template <int WARPS, int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
 __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   extern __shared__ float smem[];
@@ -91,9 +91,13 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   for (int r = 0; r < RG; ++r)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
+      // EPI_PLAIN: weight row = output column.  Fused epilogues: the weights are stored in groups of
+      // 16 rows per part (16 gate rows, their 16 up rows; 16 B, 16 C, 16 X rows), so the RG groups of
+      // a block are RG * 16 adjacent rows and stream like any 16 * RG rows.
       const int col = n0 + (EPI == EPI_PLAIN ? r * 16 : 0) + g + 8 * h;
       wok[r][h] = col < N;
-      const size_t row = (EPI == EPI_PLAIN ? 0 : (size_t)r * N) + (wok[r][h] ? col : 0);
+      const size_t row = EPI == EPI_PLAIN ? (size_t)(wok[r][h] ? col : 0)
+                                          : (size_t)blockIdx.x * (16 * RG) + r * 16 + (wok[r][h] ? g + 8 * h : 0);
       wrow[r][h] = a.W + row * a.ldw;
     }
   const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -255,10 +259,11 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
       const int ch = n0 + i;
       if (m >= M || ch >= N) continue;
       float bv = total(i, m), cv = total(16 + i, m), xval = total(32 + i, m);
-      if (a.bias) {
-        bv += a.bias[ch];
-        cv += a.bias[N + ch];
-        xval += a.bias[2 * N + ch];
+      if (a.bias) {  // stored in the weights' row order
+        const size_t base = (size_t)blockIdx.x * 48 + i;
+        bv += a.bias[base];
+        cv += a.bias[base + 16];
+        xval += a.bias[base + 32];
       }
       // rounded as the unfused path stores them, so both paths keep the same state
       const float u_new = round_bf16(bv) * round_bf16(xval);
@@ -366,20 +371,22 @@ int zk_gemm_skinny(const void* X, const float* Xf, const float* norm_w, float ep
   return ZK_EINVAL;
 }
 
-// h[M, F] = silu(x W_gate^T) * (x W_up^T), W = [gate rows; up rows] of shape [2F, K]; M <= 16.
+// h[M, F] = silu(x W_gate^T) * (x W_up^T); W [2F, K] holds groups of 16 gate rows followed by their
+// 16 up rows (F a multiple of 16); M <= 16.
 int zk_gemm_skinny_swiglu(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* H,
                           int M, int F, int K, int ldx, int ldw, int ldh, cudaStream_t stream) {
   if (M <= 0 || F <= 0) return 0;
   Args a{};
   a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = H;
   a.M = M; a.N = F; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldh;
-  if (ldh < F || check_common(a, 16)) return ZK_EINVAL;
+  if (ldh < F || F % 16 || check_common(a, 16)) return ZK_EINVAL;
   return dispatch_fused<2, EPI_SWIGLU>(a, stream);
 }
 
 // Single-token step of the short convolution: [B, C, X] = x W_in^T (+ bias), u = B*X, the causal
 // convolution over the slot's state, y = C * conv, state shifted by one.  Token m is sequence m.
-// W [3D, K]; state [slots, taps-1, D] float32; taps [taps, D]; y [M, D] bfloat16; M <= 16.
+// W [3D, K] and in_bias [3D] hold groups of 16 B rows, 16 C rows, 16 X rows (D a multiple of 16);
+// state [slots, taps-1, D] float32; taps [taps, D]; y [M, D] bfloat16; M <= 16.
 int zk_gemm_skinny_conv(const void* X, const float* Xf, const float* norm_w, float eps, const void* W,
                         const float* in_bias, float* state, const float* taps_w, const float* conv_bias,
                         const int* seq_slot, void* Y, int M, int D, int K, int taps, int ldx, int ldw, int ldy,
@@ -390,7 +397,7 @@ int zk_gemm_skinny_conv(const void* X, const float* Xf, const float* norm_w, flo
   a.M = M; a.N = D; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldy;
   a.conv_state = state; a.conv_taps = taps_w; a.conv_bias = conv_bias; a.seq_slot = seq_slot; a.taps = taps;
   a.state_stride = state_stride;
-  if (ldy < D || taps < 2 || !state || !taps_w || !seq_slot || check_common(a, 16)) return ZK_EINVAL;
+  if (ldy < D || D % 16 || taps < 2 || !state || !taps_w || !seq_slot || check_common(a, 16)) return ZK_EINVAL;
   return dispatch_fused<3, EPI_CONV>(a, stream);
 }
 

@@ -39,6 +39,7 @@ struct Params {
   int* status;
   int M, N, K;         // M tokens, N weight rows
   int ldc, accumulate, splits;
+  int swiglu;          // normal mode: W rows are groups of 16 gate rows + their 16 up rows; C [M, N/2] = silu(g)*u
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -243,22 +244,43 @@ __global__ void __launch_bounds__(THREADS)
         for (int j = 0; j < 16; ++j) stage[row * LD + c0 + j] = v[j];
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
-      if (ok) {
+      if (ok && p.swiglu) {
+        // columns of the tile: 16 gates, their 16 ups, 16 gates, ...: BN/2 outputs per row
+        const int h_base = b_tile * (BN / 2), F = p.N / 2;
+        for (int r = quarter * 32; r < quarter * 32 + 32; ++r) {
+          const int m = a_tile * BM + r;
+          if (m >= p.M) break;
+          TC* hrow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc + h_base;
+          const float* srow = stage + r * LD;
+#pragma unroll
+          for (int i = 0; i < BN / 64; ++i) {
+            const int oc = lane + 32 * i;                    // output column inside the tile
+            const int gc = (oc / 16) * 32 + (oc % 16);      // its gate's column; the up is 16 further
+            if (h_base + oc < F) {
+              const float gate = srow[gc], up = srow[gc + 16];
+              hrow[oc] = from_f32<TC>(gate / (1.0f + expf(-gate)) * up);
+            }
+          }
+        }
+      } else if (ok) {
         const int n_base = b_tile * BN;
+#pragma unroll 4
         for (int r = quarter * 32; r < quarter * 32 + 32; ++r) {
           const int m = a_tile * BM + r;
           if (m >= p.M) break;
           TC* crow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc + n_base;
           const float* srow = stage + r * LD;
           if constexpr (sizeof(TC) == 4) {
+            float o[BN / 32];
 #pragma unroll
             for (int i = 0; i < BN / 32; ++i) {
               const int col = lane + 32 * i;
-              if (n_base + col < p.N) {
-                float o = srow[col] + (p.bias ? p.bias[n_base + col] : 0.f);
-                if (p.accumulate) o += crow[col];
-                crow[col] = o;
-              }
+              o[i] = (p.accumulate && n_base + col < p.N) ? crow[col] : 0.f;   // all loads of the row first
+            }
+#pragma unroll
+            for (int i = 0; i < BN / 32; ++i) {
+              const int col = lane + 32 * i;
+              if (n_base + col < p.N) crow[col] = o[i] + srow[col] + (p.bias ? p.bias[n_base + col] : 0.f);
             }
           } else {
 #pragma unroll
@@ -401,24 +423,28 @@ int zk_gemm_tc_tickets(int N) { return ceil_div_i(N, BM); }
 
 // X [M, K], W [N, K] bfloat16, K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
 // M <= 64 runs swapped (weights on the 128-row side) with `splits` cuts of K (workspace and
-// zeroed tickets needed when splits > 1); larger M runs normal and ignores splits.
+// zeroed tickets needed when splits > 1); larger M runs normal and ignores splits.  With `swiglu`
+// (normal mode only) W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2]
+// receives silu(gate) * up (src/model.zig:1085-1117).
 int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
-               int out_dtype, int accumulate, int splits, float* workspace, unsigned* tickets, int* status,
+               int out_dtype, int accumulate, int splits, int swiglu, float* workspace, unsigned* tickets, int* status,
                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < N || !status) return ZK_EINVAL;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < (swiglu ? N / 2 : N) || !status) return ZK_EINVAL;
+  if (swiglu && (M <= 64 || N % 32 || bias || accumulate)) return ZK_EINVAL;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
   if (out_dtype != ZK_F32 && out_dtype != ZK_BF16) return ZK_EINVAL;
   Params p{};
   p.C = C; p.bias = bias; p.workspace = workspace; p.tickets = tickets; p.status = status;
-  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1; p.swiglu = swiglu;
   CUtensorMap ma, mb;
   const bool f32 = out_dtype == ZK_F32;
   if (M > 64) {
     constexpr int BN = 128;
     if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, N, K, ldw, BN)) return ZK_EINVAL;
     dim3 grid(ceil_div_i(M, BM), ceil_div_i(N, BN), 1);
-    return f32 ? launch<BN, 6, false, float>(ma, mb, p, grid, stream) : launch<BN, 6, false, bf16>(ma, mb, p, grid, stream);
+    // three stages of 32 KB: two blocks fit an SM, so one block's epilogue overlaps the other's MMAs
+    return f32 ? launch<BN, 3, false, float>(ma, mb, p, grid, stream) : launch<BN, 3, false, bf16>(ma, mb, p, grid, stream);
   }
   const int nkb = ceil_div_i(K, BK);
   splits = splits < 1 ? 1 : (splits > nkb ? nkb : splits);

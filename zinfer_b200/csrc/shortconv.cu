@@ -10,13 +10,20 @@
 // step of single tokens `conv_decode` does both at once.
 #include "common.cuh"
 
+// Column of part p (0 = B, 1 = C, 2 = X) of channel ch in a bcx row: three blocks of D columns
+// (il = 0), or groups of il channels laid out as [B (il) | C (il) | X (il)] (il > 0, the layout
+// the fused in_proj kernel wants).
+__device__ __forceinline__ size_t bcx_col(int p, int ch, int D, int il) {
+  return il ? (size_t)(ch / il) * 3 * il + (size_t)p * il + ch % il : (size_t)p * D + ch;
+}
+
 // One thread per (token, channel).
 template <typename T>
 __global__ void conv_forward_kernel(const T* __restrict__ bcx, const float* __restrict__ state,
                                     const float* __restrict__ w, const float* __restrict__ bias,
                                     const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
                                     const int* __restrict__ seq_slot, T* __restrict__ y, int n_tokens, int D, int K,
-                                    long long state_slot_stride) {
+                                    long long state_slot_stride, int il) {
   const int ch = blockIdx.y * blockDim.x + threadIdx.x;
   const int t = blockIdx.x;
   if (ch >= D || t >= n_tokens) return;
@@ -29,14 +36,14 @@ __global__ void conv_forward_kernel(const T* __restrict__ bcx, const float* __re
     float u;
     if (j >= 0) {
       const T* row = bcx + (size_t)(t - (i - j)) * 3 * D;
-      u = to_f32(row[ch]) * to_f32(row[2 * D + ch]);
+      u = to_f32(row[bcx_col(0, ch, D, il)]) * to_f32(row[bcx_col(2, ch, D, il)]);
     } else {
       u = st[(size_t)(K - 1 + j) * D + ch];
     }
     acc = fmaf(w[(size_t)k * D + ch], u, acc);
   }
   if (bias) acc += bias[ch];
-  y[(size_t)t * D + ch] = from_f32<T>(to_f32(bcx[(size_t)t * 3 * D + D + ch]) * acc);
+  y[(size_t)t * D + ch] = from_f32<T>(to_f32(bcx[(size_t)t * 3 * D + bcx_col(1, ch, D, il)]) * acc);
 }
 
 // One thread per (sequence, channel): state <- last K-1 values of u, older state rows survive
@@ -46,7 +53,7 @@ __global__ void conv_forward_kernel(const T* __restrict__ bcx, const float* __re
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                          const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int n_seqs,
-                                         int D, int K, long long state_slot_stride) {
+                                         int D, int K, long long state_slot_stride, int il) {
   const int ch = blockIdx.y * blockDim.x + threadIdx.x;
   const int b = blockIdx.x;
   if (ch >= D || b >= n_seqs) return;
@@ -58,7 +65,7 @@ __global__ void conv_state_update_kernel(const T* __restrict__ bcx, float* __res
     float u;
     if (j >= 0) {
       const T* row = bcx + (size_t)(t0 + j) * 3 * D;
-      u = to_f32(row[ch]) * to_f32(row[2 * D + ch]);
+      u = to_f32(row[bcx_col(0, ch, D, il)]) * to_f32(row[bcx_col(2, ch, D, il)]);
     } else {
       u = st[(size_t)(K - 1 + j) * D + ch];
     }
@@ -71,13 +78,13 @@ __global__ void conv_state_update_kernel(const T* __restrict__ bcx, float* __res
 template <typename T>
 __global__ void conv_decode_kernel(const T* __restrict__ bcx, float* __restrict__ state, const float* __restrict__ w,
                                    const float* __restrict__ bias, const int* __restrict__ seq_slot,
-                                   T* __restrict__ y, int n_seqs, int D, int K, long long state_slot_stride) {
+                                   T* __restrict__ y, int n_seqs, int D, int K, long long state_slot_stride, int il) {
   const int ch = blockIdx.y * blockDim.x + threadIdx.x;
   const int b = blockIdx.x;
   if (ch >= D || b >= n_seqs) return;
   float* st = state + (size_t)seq_slot[b] * state_slot_stride;
   const T* row = bcx + (size_t)b * 3 * D;
-  const float u_new = to_f32(row[ch]) * to_f32(row[2 * D + ch]);
+  const float u_new = to_f32(row[bcx_col(0, ch, D, il)]) * to_f32(row[bcx_col(2, ch, D, il)]);
   float acc = 0.f;
   for (int k = 0; k < K - 1; ++k) {
     const float u = st[(size_t)k * D + ch];
@@ -87,7 +94,7 @@ __global__ void conv_decode_kernel(const T* __restrict__ bcx, float* __restrict_
   acc = fmaf(w[(size_t)(K - 1) * D + ch], u_new, acc);
   st[(size_t)(K - 2) * D + ch] = u_new;
   if (bias) acc += bias[ch];
-  y[(size_t)b * D + ch] = from_f32<T>(to_f32(row[D + ch]) * acc);
+  y[(size_t)b * D + ch] = from_f32<T>(to_f32(row[bcx_col(1, ch, D, il)]) * acc);
 }
 
 extern "C" {
@@ -96,51 +103,51 @@ extern "C" {
 // `state_slot_stride` elements between slots; w [K, D] and bias [D] (or null) float32.
 int zk_conv_forward(const void* bcx, const float* state, const float* w, const float* bias, const int* tok_seq,
                     const int* cu_q, const int* seq_slot, void* y, int n_tokens, int D, int K,
-                    long long state_slot_stride, int dtype, cudaStream_t stream) {
+                    long long state_slot_stride, int il, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (D <= 0 || K < 2) return ZK_EINVAL;
+  if (D <= 0 || K < 2 || il < 0 || (il > 0 && D % il)) return ZK_EINVAL;
   const int threads = 128;
   dim3 grid(n_tokens, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
     conv_forward_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
-                                                             (float*)y, n_tokens, D, K, state_slot_stride);
+                                                             (float*)y, n_tokens, D, K, state_slot_stride, il);
   else if (dtype == ZK_BF16)
     conv_forward_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
-                                                            (bf16*)y, n_tokens, D, K, state_slot_stride);
+                                                            (bf16*)y, n_tokens, D, K, state_slot_stride, il);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
 }
 
 int zk_conv_state_update(const void* bcx, float* state, const int* cu_q, const int* seq_slot, int n_seqs, int D, int K,
-                         long long state_slot_stride, int dtype, cudaStream_t stream) {
+                         long long state_slot_stride, int il, int dtype, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (D <= 0 || K < 2) return ZK_EINVAL;
+  if (D <= 0 || K < 2 || il < 0 || (il > 0 && D % il)) return ZK_EINVAL;
   const int threads = 128;
   dim3 grid(n_seqs, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
     conv_state_update_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, cu_q, seq_slot, n_seqs, D,
-                                                                  K, state_slot_stride);
+                                                                  K, state_slot_stride, il);
   else if (dtype == ZK_BF16)
     conv_state_update_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, cu_q, seq_slot, n_seqs, D, K,
-                                                                 state_slot_stride);
+                                                                 state_slot_stride, il);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
 }
 
 int zk_conv_decode(const void* bcx, float* state, const float* w, const float* bias, const int* seq_slot, void* y,
-                   int n_seqs, int D, int K, long long state_slot_stride, int dtype, cudaStream_t stream) {
+                   int n_seqs, int D, int K, long long state_slot_stride, int il, int dtype, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (D <= 0 || K < 2) return ZK_EINVAL;
+  if (D <= 0 || K < 2 || il < 0 || (il > 0 && D % il)) return ZK_EINVAL;
   const int threads = 128;
   dim3 grid(n_seqs, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
     conv_decode_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, w, bias, seq_slot, (float*)y,
-                                                            n_seqs, D, K, state_slot_stride);
+                                                            n_seqs, D, K, state_slot_stride, il);
   else if (dtype == ZK_BF16)
     conv_decode_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, seq_slot, (bf16*)y, n_seqs,
-                                                           D, K, state_slot_stride);
+                                                           D, K, state_slot_stride, il);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();

@@ -25,7 +25,7 @@ _SIGNATURES = {
     "elementwise": {
         "zk_embed": "pppiiifipp",
         "zk_rmsnorm": "ppppiifip",
-        "zk_silu_mul": "ppiiip",
+        "zk_silu_mul": "ppiiiip",
         "zk_fill_normal": "pllffip",
     },
     "gemm_simt": {
@@ -39,14 +39,14 @@ _SIGNATURES = {
         "zk_gemm_skinny_fused_max_m": "",
     },
     "gemm_tc": {
-        "zk_gemm_tc": "ppppiiiiiiiiipppp",
+        "zk_gemm_tc": "ppppiiiiiiiiiipppp",
         "zk_gemm_tc_workspace_bytes": "iii",
         "zk_gemm_tc_tickets": "i",
     },
     "shortconv": {
-        "zk_conv_forward": "ppppppppiiilip",
-        "zk_conv_state_update": "ppppiiilip",
-        "zk_conv_decode": "ppppppiiilip",
+        "zk_conv_forward": "ppppppppiiiliip",
+        "zk_conv_state_update": "ppppiiiliip",
+        "zk_conv_decode": "ppppppiiiliip",
     },
     "attention_decode": {
         "zk_attn_decode": "ppppppppp" + "iiiiiiifiip",
@@ -183,15 +183,16 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return y
 
 
-def silu_mul(gu: torch.Tensor) -> torch.Tensor:
-    """h = silu(gu[:, :F]) * gu[:, F:]."""
+def silu_mul(gu: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """h = silu(gate) * up.  A row of gu is [gate (F) | up (F)], or with `interleave` = g groups of
+    g gates followed by their g ups."""
     _need(gu, "gu", (torch.float32, torch.bfloat16), (None, None))
     n, two_f = gu.shape
-    if two_f % 2:
-        raise KernelError(f"silu_mul: width {two_f} is not even")
+    if two_f % 2 or (interleave and (two_f // 2) % interleave):
+        raise KernelError(f"silu_mul: width {two_f} does not split into gate and up (groups of {interleave})")
     h = torch.empty((n, two_f // 2), dtype=gu.dtype, device=gu.device)
-    _check(_fn("elementwise", "zk_silu_mul")(_ptr(gu), _ptr(h), n, two_f // 2, dtype_code(gu.dtype), _stream()),
-           "silu_mul")
+    _check(_fn("elementwise", "zk_silu_mul")(_ptr(gu), _ptr(h), n, two_f // 2, interleave, dtype_code(gu.dtype),
+                                             _stream()), "silu_mul")
     return h
 
 
@@ -265,20 +266,26 @@ def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
-            accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1) -> torch.Tensor:
+            accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1,
+            swiglu: bool = False) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
     More than 64 rows: 128 x 128 tiles of tokens x weight rows.  Up to 64 rows: the weights take
-    the 128-row side and K is cut into `splits` parts that are added in order."""
+    the 128-row side and K is cut into `splits` parts that are added in order.  With `swiglu` (more
+    than 64 rows) w holds groups of 16 gate rows and their 16 up rows and the result is
+    silu(gate) * up, [M, N/2]."""
     if not gemm_tc_takes(a, w, out):
         raise KernelError(f"gemm_tc: a {tuple(a.shape)} / w {tuple(w.shape)} need bfloat16, K a multiple of 8 and "
                           "16-byte aligned rows")
     M, K = a.shape
     N = w.shape[0]
+    if swiglu and (M <= 64 or N % 32 or accumulate or bias is not None):
+        raise KernelError("gemm_tc: the SwiGLU epilogue needs more than 64 rows, N a multiple of 32, no bias")
+    n_out = N // 2 if swiglu else N
     if out is None:
         if accumulate:
             raise KernelError("gemm: accumulate needs an output tensor")
-        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
-    _need(out, "out", (torch.float32, torch.bfloat16), (M, N))
+        out = torch.empty((M, n_out), dtype=out_dtype or torch.bfloat16, device=a.device)
+    _need(out, "out", (torch.float32, torch.bfloat16), (M, n_out))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
     ws = None
@@ -287,7 +294,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
         ws = torch.empty(nbytes // 4, dtype=torch.float32, device=a.device)
     _check(_fn("gemm_tc", "zk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0), w.stride(0),
                                         out.stride(0), dtype_code(out.dtype), 1 if accumulate else 0, splits,
-                                        _ptr(ws), _ptr(_tickets(a.device)), _ptr(status_word(a.device)), _stream()),
+                                        1 if swiglu else 0, _ptr(ws), _ptr(_tickets(a.device)), _ptr(status_word(a.device)), _stream()),
            "gemm_tc")
     return out
 
@@ -364,8 +371,9 @@ def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtyp
 
 
 def gemm_skinny_swiglu(a, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """h = silu(a W_gate^T) * (a W_up^T) in one kernel; w_gate_up [2F, K] = gate rows, then up rows."""
-    if not gemm_skinny_fused_takes(a, w_gate_up) or w_gate_up.shape[0] % 2:
+    """h = silu(a W_gate^T) * (a W_up^T) in one kernel; w_gate_up [2F, K] holds groups of 16 gate
+    rows followed by their 16 up rows."""
+    if not gemm_skinny_fused_takes(a, w_gate_up) or w_gate_up.shape[0] % 32:
         raise KernelError("gemm_skinny_swiglu: at most 16 rows, K a multiple of 8, 16-byte aligned rows")
     X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
     F = w_gate_up.shape[0] // 2
@@ -379,8 +387,9 @@ def gemm_skinny_swiglu(a, w_gate_up: torch.Tensor) -> torch.Tensor:
 def gemm_skinny_conv(a, w_in: torch.Tensor, in_bias, state: torch.Tensor, taps: torch.Tensor, conv_bias,
                      seq_slot: torch.Tensor) -> torch.Tensor:
     """Single-token step of the gated short convolution fused with its in_proj: row m of `a` is
-    sequence m; `state` [slots, K-1, D] is shifted by one; returns y [M, D]."""
-    if not gemm_skinny_fused_takes(a, w_in) or w_in.shape[0] % 3:
+    sequence m; `state` [slots, K-1, D] is shifted by one; returns y [M, D].  w_in [3D, K] and
+    in_bias [3D] hold groups of 16 B rows, 16 C rows, 16 X rows."""
+    if not gemm_skinny_fused_takes(a, w_in) or w_in.shape[0] % 48:
         raise KernelError("gemm_skinny_conv: at most 16 rows, K a multiple of 8, 16-byte aligned rows")
     X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
     D = w_in.shape[0] // 3
@@ -402,9 +411,10 @@ def gemm_skinny_conv(a, w_in: torch.Tensor, in_bias, state: torch.Tensor, taps: 
 
 # ------------------------------------------------------------------------------- short convolution
 
-def conv_forward(bcx, state, w, bias, tok_seq, cu_q, seq_slot) -> torch.Tensor:
+def conv_forward(bcx, state, w, bias, tok_seq, cu_q, seq_slot, interleave: int = 0) -> torch.Tensor:
     """y of the gated short convolution for a packed batch; reads `state`, does not change it.
-    bcx [n, 3D]; state [slots, K-1, D] float32; w [K, D] float32; bias [D] float32 or None."""
+    bcx [n, 3D] = [B | C | X] (or groups of `interleave` channels as [B | C | X]); state
+    [slots, K-1, D] float32; w [K, D] float32; bias [D] float32 or None."""
     _need(bcx, "bcx", (torch.float32, torch.bfloat16), (None, None))
     n, three_d = bcx.shape
     D = three_d // 3
@@ -417,22 +427,22 @@ def conv_forward(bcx, state, w, bias, tok_seq, cu_q, seq_slot) -> torch.Tensor:
         _need(t, nm, torch.int32)
     y = torch.empty((n, D), dtype=bcx.dtype, device=bcx.device)
     _check(_fn("shortconv", "zk_conv_forward")(_ptr(bcx), _ptr(state), _ptr(w), _ptr(bias), _ptr(tok_seq), _ptr(cu_q),
-                                               _ptr(seq_slot), _ptr(y), n, D, K, state.stride(0),
+                                               _ptr(seq_slot), _ptr(y), n, D, K, state.stride(0), interleave,
                                                dtype_code(bcx.dtype), _stream()), "conv_forward")
     return y
 
 
-def conv_state_update(bcx, state, cu_q, seq_slot, n_seqs: int, K: int) -> None:
+def conv_state_update(bcx, state, cu_q, seq_slot, n_seqs: int, K: int, interleave: int = 0) -> None:
     """state[slot] <- the last K-1 values of B*X of each sequence (older rows kept if fewer came)."""
     _need(bcx, "bcx", (torch.float32, torch.bfloat16), (None, None))
     D = bcx.shape[1] // 3
     _need(state, "conv state", torch.float32, (None, K - 1, D))
     _check(_fn("shortconv", "zk_conv_state_update")(_ptr(bcx), _ptr(state), _ptr(cu_q), _ptr(seq_slot), n_seqs, D, K,
-                                                    state.stride(0), dtype_code(bcx.dtype), _stream()),
+                                                    state.stride(0), interleave, dtype_code(bcx.dtype), _stream()),
            "conv_state_update")
 
 
-def conv_decode(bcx, state, w, bias, seq_slot) -> torch.Tensor:
+def conv_decode(bcx, state, w, bias, seq_slot, interleave: int = 0) -> torch.Tensor:
     """Single-token step: y and the shifted state in one kernel; row b of bcx is sequence b."""
     _need(bcx, "bcx", (torch.float32, torch.bfloat16), (None, None))
     n, three_d = bcx.shape
@@ -445,7 +455,8 @@ def conv_decode(bcx, state, w, bias, seq_slot) -> torch.Tensor:
     _need(seq_slot, "seq_slot", torch.int32)
     y = torch.empty((n, D), dtype=bcx.dtype, device=bcx.device)
     _check(_fn("shortconv", "zk_conv_decode")(_ptr(bcx), _ptr(state), _ptr(w), _ptr(bias), _ptr(seq_slot), _ptr(y), n,
-                                              D, K, state.stride(0), dtype_code(bcx.dtype), _stream()), "conv_decode")
+                                              D, K, state.stride(0), interleave, dtype_code(bcx.dtype), _stream()),
+           "conv_decode")
     return y
 
 

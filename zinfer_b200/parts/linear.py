@@ -38,6 +38,20 @@ class NormedRows:
         return kernels.NormInput(self.x, self.weight, self.eps)
 
 
+FUSION_GROUP = 16     # rows per part and group in the interleaved weight layouts of the fused kernels
+
+
+def interleave_rows(parts, group: int = FUSION_GROUP) -> torch.Tensor:
+    """Rows of equally shaped matrices (or vectors) regrouped as `group` rows of the first, the
+    same `group` rows of the second, ...: a block of a fused kernel then finds all parts of its
+    outputs in adjacent rows.  The row count must be a multiple of `group`."""
+    n = parts[0].shape[0]
+    if n % group or any(p.shape != parts[0].shape for p in parts):
+        raise ValueError(f"cannot interleave {[tuple(p.shape) for p in parts]} in groups of {group}")
+    stacked = torch.stack([p.reshape(n // group, group, *p.shape[1:]) for p in parts], dim=1)
+    return stacked.reshape(len(parts) * n, *parts[0].shape[1:]).contiguous()
+
+
 def as_tensor(a: Union[torch.Tensor, NormedRows]) -> torch.Tensor:
     return a.tensor() if isinstance(a, NormedRows) else a
 
