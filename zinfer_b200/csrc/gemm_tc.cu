@@ -328,12 +328,13 @@ __global__ void __launch_bounds__(THREADS)
           for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * BM + row] = v[j];
         } else if (n < p.N) {
           const float b = p.bias ? p.bias[n] : 0.f;
-          for (int j = 0; j < 16 && c0 + j < p.M; ++j) {
-            TC* dst = C + (size_t)(c0 + j) * p.ldc + n;
-            float o = v[j] + b;
-            if (p.accumulate) o += to_f32(*dst);
-            *dst = from_f32<TC>(o);
-          }
+          float old[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)   // all loads first: they do not depend on one another
+            old[j] = (p.accumulate && c0 + j < p.M) ? to_f32(C[(size_t)(c0 + j) * p.ldc + n]) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < p.M) C[(size_t)(c0 + j) * p.ldc + n] = from_f32<TC>(v[j] + b + old[j]);
         }
       }
       if (p.splits > 1) {
@@ -351,12 +352,24 @@ __global__ void __launch_bounds__(THREADS)
           if (n < p.N) {
             const float b = p.bias ? p.bias[n] : 0.f;
             const float* base = p.workspace + (size_t)tile_id * p.splits * (BN * BM);
-            for (int t = 0; t < p.M; ++t) {
-              float o = b;
-              for (int z = 0; z < p.splits; ++z) o += __ldcg(base + (size_t)z * (BN * BM) + (size_t)t * BM + row);
-              TC* dst = C + (size_t)t * p.ldc + n;
-              if (p.accumulate) o += to_f32(*dst);
-              *dst = from_f32<TC>(o);
+            for (int t0 = 0; t0 < p.M; t0 += 8) {
+              float acc[8], old[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                acc[j] = b;
+                old[j] = (p.accumulate && t0 + j < p.M) ? to_f32(C[(size_t)(t0 + j) * p.ldc + n]) : 0.f;
+              }
+              for (int z = 0; z < p.splits; ++z) {   // split order: the same bits each run
+                float part_v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  part_v[j] = (t0 + j < p.M) ? __ldcg(base + (size_t)z * (BN * BM) + (size_t)(t0 + j) * BM + row) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += part_v[j];
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (t0 + j < p.M) C[(size_t)(t0 + j) * p.ldc + n] = from_f32<TC>(acc[j] + old[j]);
             }
           }
         }
