@@ -12,9 +12,11 @@
 // Two roles of the operands:
 //   normal : rows of the tile are tokens (X), columns are weight rows (W): prompt steps;
 //   swapped: rows of the tile are weight rows, columns are the few tokens of a single-token
-//            step (16..64): every weight is read once, and K may be split over blockIdx.z so
-//            that all SMs stream; partial tiles go through a float32 workspace and the block
-//            that arrives last adds them in split order (no atomics on data, same bits each run).
+//            step (16..64): every weight is read once, and K may be split over the 2, 4 or 8
+//            blocks of a thread-block cluster so that more SMs stream; each block leaves its
+//            partial tile in its own shared memory, and after a cluster barrier every block adds
+//            the partials of its share of the tokens in split order, reading the other blocks'
+//            shared memory directly (no workspace, no atomics, the same bits each run).
 // Accumulation is float32 in tensor memory.  (Reference: the matmul driver with its accumulate
 // flag, src/model.zig:903-1026, 918-920.)
 //
@@ -34,8 +36,6 @@ constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds of SM clo
 struct Params {
   void* C;
   const float* bias;
-  float* workspace;    // swapped with splits: [tiles][splits][BN][128] float32
-  unsigned* tickets;   // [tiles], zero before the launch and zero again after it
   int* status;
   int M, N, K;         // M tokens, N weight rows
   int ldc, accumulate, splits;
@@ -112,6 +112,24 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float v[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Thread-block cluster: barrier over all threads of all blocks, rank, and loads from another
+// block's shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ld_remote_f32(unsigned local_smem_addr, unsigned rank) {
+  unsigned remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
 // groups of 8 rows 1024 bytes apart (stride byte offset), version 1, swizzle mode 2.
 __device__ __forceinline__ unsigned long long smem_desc(const void* tile) {
@@ -148,7 +166,6 @@ __global__ void __launch_bounds__(THREADS)
   unsigned long long* acc_done = empty + STAGES;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_done + 1);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  unsigned* last_flag = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a_tile = blockIdx.x, b_tile = blockIdx.y, split = blockIdx.z;
@@ -165,7 +182,6 @@ __global__ void __launch_bounds__(THREADS)
     }
     mbar_init(acc_done, 1);
     *aborted = 0;
-    *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -312,8 +328,7 @@ __global__ void __launch_bounds__(THREADS)
       // rows are weight rows n, columns are tokens; a warp's lanes are 32 consecutive n
       const int n = a_tile * BM + row;
       TC* C = reinterpret_cast<TC*>(p.C);
-      const int tile_id = a_tile;
-      float* part = p.splits > 1 ? p.workspace + ((size_t)tile_id * p.splits + split) * (BN * BM) : nullptr;
+      float* part = reinterpret_cast<float*>(tiles);   // [BN][128] partial tile (the stages are free by now)
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
@@ -325,7 +340,7 @@ __global__ void __launch_bounds__(THREADS)
         }
         if (p.splits > 1) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * BM + row] = v[j];
+          for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = v[j];
         } else if (n < p.N) {
           const float b = p.bias ? p.bias[n] : 0.f;
           float old[16];
@@ -337,43 +352,39 @@ __global__ void __launch_bounds__(THREADS)
             if (c0 + j < p.M) C[(size_t)(c0 + j) * p.ldc + n] = from_f32<TC>(v[j] + b + old[j]);
         }
       }
-      if (p.splits > 1) {
-        // the block that arrives last adds the partial tiles in split order
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
-        if (threadIdx.x == 64) {
-          const unsigned prev = atomicAdd(&p.tickets[tile_id], 1u);
-          *last_flag = (prev == (unsigned)p.splits - 1) ? 1u : 0u;
-          if (prev == (unsigned)p.splits - 1) p.tickets[tile_id] = 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          __threadfence();
-          if (n < p.N) {
-            const float b = p.bias ? p.bias[n] : 0.f;
-            const float* base = p.workspace + (size_t)tile_id * p.splits * (BN * BM);
-            for (int t0 = 0; t0 < p.M; t0 += 8) {
-              float acc[8], old[8];
+    }
+  }
+
+  if constexpr (SWAP) {
+    if (p.splits > 1) {
+      // Every block of the cluster has its partial tile in shared memory; block r adds, in split
+      // order, the partials of the tokens r, r + splits, ... and writes them.
+      __syncwarp();
+      cluster_sync_all();
+      if (warp >= 2) {
+        const int row = (warp & 3) * 32 + lane;
+        const int n = a_tile * BM + row;
+        TC* C = reinterpret_cast<TC*>(p.C);
+        const unsigned base = smem_u32(tiles);
+        const unsigned rank = cluster_rank();
+        if (n < p.N) {
+          const float b = p.bias ? p.bias[n] : 0.f;
+          for (int t = (int)rank; t < p.M; t += p.splits) {
+            float pv[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                acc[j] = b;
-                old[j] = (p.accumulate && t0 + j < p.M) ? to_f32(C[(size_t)(t0 + j) * p.ldc + n]) : 0.f;
-              }
-              for (int z = 0; z < p.splits; ++z) {   // split order: the same bits each run
-                float part_v[8];
+            for (int z = 0; z < 8; ++z)   // up to 8 blocks in a cluster; the loads are independent
+              pv[z] = z < p.splits ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
+            TC* dst = C + (size_t)t * p.ldc + n;
+            const float old = p.accumulate ? to_f32(*dst) : 0.f;
+            float acc = b;
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  part_v[j] = (t0 + j < p.M) ? __ldcg(base + (size_t)z * (BN * BM) + (size_t)(t0 + j) * BM + row) : 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] += part_v[j];
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (t0 + j < p.M) C[(size_t)(t0 + j) * p.ldc + n] = from_f32<TC>(acc[j] + old[j]);
-            }
+            for (int z = 0; z < 8; ++z) acc += pv[z];
+            *dst = from_f32<TC>(acc + old);
           }
         }
       }
+      __syncwarp();
+      cluster_sync_all();   // nobody leaves while its shared memory may still be read
     }
   }
 
@@ -418,37 +429,39 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
   const size_t smem = Smem<BN, STAGES>::BYTES;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  kern<<<grid, THREADS, smem, stream>>>(ma, mb, p);
-  return ZK_LAUNCH_STATUS();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;   // the blocks that split K form one cluster
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.splits > 1 ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
 }
 
 }  // namespace
 
 extern "C" {
 
-// Bytes of float32 workspace and number of tickets a swapped launch with `splits` needs.
-long long zk_gemm_tc_workspace_bytes(int M, int N, int splits) {
-  if (splits <= 1) return 0;
-  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-  return (long long)ceil_div_i(N, BM) * splits * bn * BM * 4;
-}
-int zk_gemm_tc_tickets(int N) { return ceil_div_i(N, BM); }
-
 // X [M, K], W [N, K] bfloat16, K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
-// M <= 64 runs swapped (weights on the 128-row side) with `splits` cuts of K (workspace and
-// zeroed tickets needed when splits > 1); larger M runs normal and ignores splits.  With `swiglu`
+// M <= 64 runs swapped (weights on the 128-row side) with K cut into `splits` parts (rounded down
+// to 1, 2, 4 or 8: a cluster's size); larger M runs normal and ignores splits.  With `swiglu`
 // (normal mode only) W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2]
 // receives silu(gate) * up (src/model.zig:1085-1117).
 int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
-               int out_dtype, int accumulate, int splits, int swiglu, float* workspace, unsigned* tickets, int* status,
-               cudaStream_t stream) {
+               int out_dtype, int accumulate, int splits, int swiglu, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < (swiglu ? N / 2 : N) || !status) return ZK_EINVAL;
   if (swiglu && (M <= 64 || N % 32 || bias || accumulate)) return ZK_EINVAL;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
   if (out_dtype != ZK_F32 && out_dtype != ZK_BF16) return ZK_EINVAL;
   Params p{};
-  p.C = C; p.bias = bias; p.workspace = workspace; p.tickets = tickets; p.status = status;
+  p.C = C; p.bias = bias; p.status = status;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1; p.swiglu = swiglu;
   CUtensorMap ma, mb;
   const bool f32 = out_dtype == ZK_F32;
@@ -460,10 +473,11 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
     return f32 ? launch<BN, 3, false, float>(ma, mb, p, grid, stream) : launch<BN, 3, false, bf16>(ma, mb, p, grid, stream);
   }
   const int nkb = ceil_div_i(K, BK);
-  splits = splits < 1 ? 1 : (splits > nkb ? nkb : splits);
-  while (splits > 1 && ceil_div_i(nkb, splits) * (splits - 1) >= nkb) --splits;  // no empty split
-  if (splits > 1 && (!workspace || !tickets)) return ZK_EINVAL;
-  p.splits = splits;
+  int s2 = 1;
+  while (s2 * 2 <= splits && s2 * 2 <= 8 && s2 * 2 <= nkb) s2 *= 2;
+  while (s2 > 1 && ceil_div_i(nkb, s2) * (s2 - 1) >= nkb) s2 /= 2;  // no empty split
+  p.splits = s2;
+  splits = s2;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   if (!make_map(&ma, W, N, K, ldw, BM) || !make_map(&mb, X, M, K, ldx, bn)) return ZK_EINVAL;
   dim3 grid(ceil_div_i(N, BM), 1, splits);

@@ -39,9 +39,7 @@ _SIGNATURES = {
         "zk_gemm_skinny_fused_max_m": "",
     },
     "gemm_tc": {
-        "zk_gemm_tc": "ppppiiiiiiiiiipppp",
-        "zk_gemm_tc_workspace_bytes": "iii",
-        "zk_gemm_tc_tickets": "i",
+        "zk_gemm_tc": "ppppiiiiiiiiiipp",
     },
     "shortconv": {
         "zk_conv_forward": "ppppppppiiiliip",
@@ -76,7 +74,7 @@ _SIGNATURES = {
 }
 
 
-_RESTYPES = {"zk_gemm_tc_workspace_bytes": ctypes.c_longlong, "zk_attn_decode_noalloc_bytes": ctypes.c_longlong}
+_RESTYPES = {"zk_attn_decode_noalloc_bytes": ctypes.c_longlong}
 
 
 class KernelError(RuntimeError):
@@ -241,16 +239,7 @@ def status_word(device) -> torch.Tensor:
     st = _device_state.setdefault(dev, {})
     if "status" not in st:
         st["status"] = torch.zeros(1, dtype=torch.int32, device=dev)
-        st["tickets"] = torch.zeros(4096, dtype=torch.int32, device=dev)
     return st["status"]
-
-
-def _tickets(device) -> torch.Tensor:
-    status_word(device)
-    dev = torch.device(device)
-    if dev.index is None:
-        dev = torch.device("cuda", torch.cuda.current_device())
-    return _device_state[dev]["tickets"]
 
 
 def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
@@ -270,7 +259,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
             swiglu: bool = False) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
     More than 64 rows: 128 x 128 tiles of tokens x weight rows.  Up to 64 rows: the weights take
-    the 128-row side and K is cut into `splits` parts that are added in order.  With `swiglu` (more
+    the 128-row side and K is cut into `splits` (1, 2, 4 or 8) parts, one per block of a cluster,
+    that are added in order.  With `swiglu` (more
     than 64 rows) w holds groups of 16 gate rows and their 16 up rows and the result is
     silu(gate) * up, [M, N/2]."""
     if not gemm_tc_takes(a, w, out):
@@ -288,13 +278,9 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     _need(out, "out", (torch.float32, torch.bfloat16), (M, n_out))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
-    ws = None
-    if M <= 64 and splits > 1:
-        nbytes = _fn("gemm_tc", "zk_gemm_tc_workspace_bytes")(M, N, splits)
-        ws = torch.empty(nbytes // 4, dtype=torch.float32, device=a.device)
     _check(_fn("gemm_tc", "zk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0), w.stride(0),
                                         out.stride(0), dtype_code(out.dtype), 1 if accumulate else 0, splits,
-                                        1 if swiglu else 0, _ptr(ws), _ptr(_tickets(a.device)), _ptr(status_word(a.device)), _stream()),
+                                        1 if swiglu else 0, _ptr(status_word(a.device)), _stream()),
            "gemm_tc")
     return out
 

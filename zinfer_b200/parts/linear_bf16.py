@@ -10,19 +10,27 @@ from .. import kernels
 
 
 # Between 17 and 64 rows the tcgen05 kernel with the weights on its 128-row side beats the mma.sync
-# kernel once the weight matrix gives it enough blocks (measured at 64 rows: 18 us against 44 us
-# for N = 16384, 15 us against 22 us for N = 6144, 15 us against 12 us for N = 2048).
+# kernel (measured at 64 rows on the LFM2-1.2B shapes: 18 us against 44 us for N = 16384, 13 against
+# 22 for N = 6144, 9 against 12 for N = 2048, 14 against 38 for N = 2048 with K = 8192); up to 8 rows
+# the mma.sync kernel is as fast or faster.  K is split over a cluster when the weight matrix alone
+# gives fewer 128-row tiles than there are SMs.
 TC_SWAPPED_MIN_ROWS = 17
-TC_SWAPPED_MIN_N = 4096
+
+
+def swapped_splits(n_weight_rows: int) -> int:
+    tiles = -(-n_weight_rows // 128)
+    want = max(1, min(8, 192 // tiles))
+    return 1 << (want.bit_length() - 1)
 
 
 def try_linear(a, w, out, out_dtype, accumulate, bias):
     from .linear import as_tensor, fused_input
 
-    if TC_SWAPPED_MIN_ROWS <= a.shape[0] <= kernels.gemm_skinny_max_m() and w.shape[0] >= TC_SWAPPED_MIN_N:
+    if TC_SWAPPED_MIN_ROWS <= a.shape[0] <= kernels.gemm_skinny_max_m():
         t = as_tensor(a)
         if kernels.gemm_tc_takes(t, w, out):
-            return kernels.gemm_tc(t, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)
+            return kernels.gemm_tc(t, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias,
+                                   splits=swapped_splits(w.shape[0]))
     x = fused_input(a, w)
     if x is not None:
         return kernels.gemm_skinny(x, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)
