@@ -43,6 +43,17 @@ TINY = {
                     conv_L_cache=2, conv_bias=False, rope_theta=50000.0, norm_eps=3e-6,
                     tie_word_embeddings=True, eos_token_id=2),
         seed=37, norm_init="one_plus_normal", storage="float32"),
+    # head size 64 with four heads per KV head and sizes in multiples of 16: the shapes for which the
+    # tensor-core attention kernels, the fused epilogues and the tcgen05 contractions are chosen
+    "tiny_d": dict(
+        config=dict(architectures=["Lfm2ForCausalLM"], model_type="lfm2", vocab_size=1000, hidden_size=256,
+                    num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+                    max_position_embeddings=1024,
+                    layer_types=["conv", "full_attention", "conv", "full_attention"],
+                    block_ff_dim=768, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0,
+                    block_multiple_of=256, conv_L_cache=3, conv_bias=False, rope_theta=1000000.0, norm_eps=1e-5,
+                    tie_word_embeddings=True, eos_token_id=7),
+        seed=41, norm_init="one_plus_normal", storage="bfloat16"),
 }
 
 

@@ -10,7 +10,8 @@ from plain_lfm2 import PlainLfm2
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny_a": [5, 11, 17, 40, 70], "tiny_b": [1, 2, 9, 33, 64, 100], "tiny_c": [3, 29, 66, 130, 47]}
+LENGTHS = {"tiny_a": [5, 11, 17, 40, 70], "tiny_b": [1, 2, 9, 33, 64, 100], "tiny_c": [3, 29, 66, 130, 47],
+           "tiny_d": [200, 7, 65, 130, 33]}
 DECODE_TAIL = 32
 
 
@@ -97,4 +98,5 @@ def test_replay_all_cuts(model_folders, tmp_path, name, dtype):
         e = np.max(np.abs(got[step][row].astype(np.float64) - ref[rid][pos])) / np.max(np.abs(ref[rid]))
         if e > worst:
             worst, where = e, (step, row, rid, pos, steps[step]["entries"][0]["id"])
+    print(f"replay {name} {dtype}: worst error {worst:.3e} of max |logit| (tolerance {helpers.TOL[dtype]:.0e})")
     assert worst <= helpers.TOL[dtype], f"{name} {dtype}: worst error {worst:.3e} at (step,row,req,pos,first id) {where}"
