@@ -114,7 +114,25 @@ def model_numbers(cfg, n_layers_run: int) -> dict:
             "kv_bytes_per_token": n_attn * 2 * KV * 2, "conv_state_bytes": (len(kinds) - n_attn) * (cfg.conv_L_cache - 1) * D * 4}
 
 
-def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int):
+def print_op_trace(engine, batch: int) -> None:
+    """Where block 0 of the persistent single-token kernel spends a step, by kind of operation."""
+    plan = engine._fused[batch].plan
+    if not plan:
+        print("the model's single-token step is not fused", file=sys.stderr)
+        return
+    kinds: dict = {}
+    for row in plan.trace(engine.last_fused_ctx):
+        k = kinds.setdefault(row["op"], [0, 0.0, 0.0, 0.0])
+        k[0] += 1
+        for i, name in enumerate(("stage_us", "work_us", "barrier_us")):
+            k[i + 1] += row[name]
+    print(f"{'operation':28s} count  stage   work  barrier  (mean us)    sum us", file=sys.stderr)
+    for name, (n, a, b, c) in kinds.items():
+        print(f"{name:28s} {n:5d} {a / n:6.2f} {b / n:6.2f} {c / n:8.2f} {a + b + c:19.1f}", file=sys.stderr)
+    engine.status.zero_()
+
+
+def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int, trace_ops: bool = False):
     """Prefills `batch` prompts of lengths uniform in PROMPT_RANGE, then times `steps` decode steps.
     Returns (ms per step, total cached tokens at the middle of the timed region, launches per step)."""
     from zinfer_b200 import kernels
@@ -140,6 +158,8 @@ def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: 
         engine.check_status()
         ms = start.elapsed_time(stop) / steps
         cached = sum(lens) + batch * (warmup + steps // 2)
+        if trace_ops and engine.last_fused_ctx is not None:
+            print_op_trace(engine, batch)
     finally:
         engine.finish(slots)
     return ms, cached, launches
@@ -186,7 +206,7 @@ def own_arm(args) -> dict:
     model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True)
     B = args.batch
     engine = z.Engine(model, max_batch=64, max_seq_len=CONTEXT, max_tokens=64 * CONTEXT, page_size=64,
-                      use_graphs=not args.no_graphs)
+                      use_graphs=not args.no_graphs, fused_decode=args.fused)
     if args.only == "prefill":
         return {"prefill": time_prefill(engine, torch, np.random.default_rng(0), cfg, args.warmup,
                                         model_numbers(cfg, cfg.num_hidden_layers), pk)}
@@ -196,7 +216,8 @@ def own_arm(args) -> dict:
 
     # decode at the headline batch, device-timed, with the clocks sampled meanwhile
     with ClockSampler() as clocks:
-        ms, cached, launches = time_decode(engine, torch, rng, B, args.steps, args.warmup, cfg.vocab_size)
+        ms, cached, launches = time_decode(engine, torch, rng, B, args.steps, args.warmup, cfg.vocab_size,
+                                           trace_ops=args.trace_ops)
     value = B / (ms * 1e-3)
     step_bytes = weight_bytes + cached * num["kv_bytes_per_token"] + B * num["conv_state_bytes"] * 2
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -259,6 +280,9 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only (for profiling); the JSON line then lacks the other parts")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--trace-ops", action="store_true",
+                    help="with --fused --only decode: print where block 0 of the persistent kernel spends a step")
+    ap.add_argument("--fused", action="store_true", help="run decode steps of up to 16 sequences as one persistent kernel")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

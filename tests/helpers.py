@@ -4,7 +4,8 @@ tiny_a and tiny_b are the two configurations that differ in every size and optio
 kind, head counts and group size, head size, feed-forward rule, conv window and bias, rope
 base, eps, tied or untied head, norm-weight init, vocabulary); tiny_c adds a windowed
 attention group next to a full one, a width and vocabulary that are no power of two, a
-two-tap convolution and a float32 weight file.
+two-tap convolution and a float32 weight file; tiny_d and tiny_e have the head size 64 that the
+tensor-core attention and the one-kernel single-token step take, and differ in the rest.
 """
 from __future__ import annotations
 
@@ -54,6 +55,16 @@ TINY = {
                     block_multiple_of=256, conv_L_cache=3, conv_bias=False, rope_theta=1000000.0, norm_eps=1e-5,
                     tie_word_embeddings=True, eos_token_id=7),
         seed=41, norm_init="one_plus_normal", storage="bfloat16"),
+    # head size 64 again, otherwise unlike tiny_d: two heads per KV head, a windowed layer first, four
+    # taps with a bias, an untied head over a vocabulary that is no power of two, a width of 192
+    "tiny_e": dict(
+        config=dict(architectures=["Lfm2ForCausalLM"], model_type="lfm2", vocab_size=777, hidden_size=192,
+                    num_hidden_layers=5, num_attention_heads=6, num_key_value_heads=3, head_dim=64,
+                    max_position_embeddings=512,
+                    layer_types=["sliding_attention", "conv", "conv", "full_attention", "sliding_attention"],
+                    sliding_window=40, block_ff_dim=320, block_auto_adjust_ff_dim=False, conv_L_cache=4,
+                    conv_bias=True, rope_theta=10000.0, norm_eps=1e-6, tie_word_embeddings=False, eos_token_id=[1, 9]),
+        seed=53, norm_init="normal", storage="bfloat16"),
 }
 
 

@@ -11,7 +11,7 @@ from plain_lfm2 import PlainLfm2
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": [5, 11, 17, 40, 70], "tiny_b": [1, 2, 9, 33, 64, 100], "tiny_c": [3, 29, 66, 130, 47],
-           "tiny_d": [200, 7, 65, 130, 33]}
+           "tiny_d": [200, 7, 65, 130, 33], "tiny_e": [90, 41, 3, 150, 64]}
 DECODE_TAIL = 32
 
 

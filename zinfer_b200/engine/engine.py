@@ -19,6 +19,7 @@ from .. import kernels
 from ..cache.manager import CacheManager
 from ..models.model import Model
 from .context import CallContext, StepContext, batch_layout, pack_batch
+from .fused_decode import build as build_fused_plan
 
 
 class StepError(RuntimeError):
@@ -29,30 +30,60 @@ class StepError(RuntimeError):
 _STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's position has no cache page",
                 11: "a tensor-core contraction gave up waiting for a free pipeline stage",
                 12: "a tensor-core contraction gave up waiting for its operand tiles",
-                13: "a tensor-core contraction gave up waiting for its accumulator"}
+                13: "a tensor-core contraction gave up waiting for its accumulator",
+                21: "the one-kernel single-token step gave up waiting at a grid barrier",
+                22: "the one-kernel single-token step was given an operation it does not take"}
 
 
 class _DecodeGraph:
-    """A captured single-token step for one batch size: static input buffer, static output."""
+    """A captured single-token step for one batch size: static input buffer, static output.
 
-    def __init__(self, meta_host, meta_dev, want_rows):
-        self.meta_host, self.meta_dev, self.want_rows = meta_host, meta_dev, want_rows
+    The batch's description reaches the static device buffer through a small ring of pinned
+    host buffers: a buffer is rewritten only after the copy that last read it has run, so a host
+    that runs several steps ahead of the device cannot change a step's input under it."""
+
+    RING = 4
+
+    def __init__(self, words, device):
+        self.meta_dev = torch.zeros(words, dtype=torch.int32, device=device)
+        self._hosts = [torch.zeros(words, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self._copied = [None] * self.RING
+        self._next = 0
         self.tiles: dict = {}
+        self.plan = None            # engine.fused_decode.FusedDecodePlan, or False if the model cannot be fused
         self.warmed = False
         self.graph = None
         self.logits = None
+
+    def upload(self, words) -> None:
+        """Copies the packed batch description to the static device buffer."""
+        i = self._next
+        self._next = (i + 1) % self.RING
+        if self._copied[i] is not None:
+            self._copied[i].synchronize()
+        self._hosts[i].numpy()[:] = words
+        self.meta_dev.copy_(self._hosts[i], non_blocking=True)
+        if self._copied[i] is None:
+            self._copied[i] = torch.cuda.Event()
+        self._copied[i].record()
 
 
 class Engine:
     def __init__(self, model: Model, max_batch: int = 64, max_seq_len: Optional[int] = None,
                  max_tokens: Optional[int] = None, page_size: int = 64, max_step_tokens: int = 8192,
-                 attn_split_keys: int = 0, use_graphs: bool = True):
+                 attn_split_keys: int = 0, use_graphs: bool = True, fused_decode: bool = False,
+                 fused_decode_max_context: int = 4096):
         """max_batch: slots (sequences alive at once).  max_seq_len: longest sequence, default
         the model's max_position_embeddings.  max_tokens: tokens the cache holds in total, each
         sequence rounded up to whole pages; default max_batch * max_seq_len.  max_step_tokens:
         a step with more tokens runs as several packed chunks.  attn_split_keys: keys per
         chunk of single-token attention (0 = chosen per step).  use_graphs: replay single-token
-        steps of `decode` from CUDA graphs."""
+        steps of `decode` from CUDA graphs.  fused_decode: run single-token steps of few sequences
+        as one persistent kernel where the model's parts allow it (engine/fused_decode.py), while
+        no sequence is longer than fused_decode_max_context (that kernel does not split a
+        sequence's keys over blocks).  Off by default: measured on a B200 it is slower than the
+        graph of separate kernels (its per-operation barrier and input staging cost what a kernel
+        boundary costs, and its contraction loop issues more instructions per byte)."""
         kernels.require_cuda()
         if model.device is None:
             raise ValueError("the model has no weights loaded")
@@ -71,6 +102,10 @@ class Engine:
         self.status = kernels.status_word(self.device)      # one status word per device, shared by all kernels
         self.vocab_size = cfg.vocab_size
         self.use_graphs = bool(use_graphs)
+        self.fused_decode = bool(fused_decode) and self.use_graphs
+        self.fused_decode_max_context = int(fused_decode_max_context)
+        self._fused: dict[int, _DecodeGraph] = {}
+        self.last_fused_ctx = None      # batch of the last fused step (FusedDecodePlan.trace takes it)
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self.stats = None
@@ -174,10 +209,11 @@ class Engine:
     def decode(self, slots: Sequence[int], tokens: Sequence[int], check: bool = False) -> torch.Tensor:
         """One token for each sequence, logits [len(slots), vocab] for all of them.  The same
         computation as `step(slots, [[t] for t in tokens])`, replayed from a CUDA graph: a step of
-        single tokens is some 150 small kernels, and launching them one by one costs more than
+        single tokens is some hundred small kernels, and launching them one by one costs more than
         running them.  One graph per (batch size, key-chunk layout); its first use runs
-        eagerly (which also loads every kernel), its second use is captured.  The returned
-        tensor is the graph's output buffer: use it before the next call."""
+        eagerly (which also loads every kernel), its second use is captured.  With
+        `fused_decode` the step is one launch of the persistent kernel instead.  The returned
+        tensor is a static output buffer: use it before the next call."""
         if not self.use_graphs:
             return self.step(slots, [[int(t)] for t in tokens], check=check)
         B = len(slots)
@@ -187,34 +223,44 @@ class Engine:
         self.cache.reserve(slots, ones)
         self.cache.sync()
         starts = [int(self.cache.lengths[s]) for s in slots]
-        max_kv = -(-(max(starts) + 1) // 512) * 512            # bucketed, so that the key changes rarely
-        key = (B, max_kv)
-        entry = self._graphs.get(key)
-        if entry is None:
-            lay = batch_layout(B, B)["_total"][0]
-            entry = _DecodeGraph(torch.zeros(lay, dtype=torch.int32).pin_memory(),
-                                 torch.zeros(lay, dtype=torch.int32, device=self.device),
-                                 torch.arange(B, dtype=torch.int32, device=self.device))
-            self._graphs[key] = entry
-        entry.meta_host.numpy()[:] = pack_batch(slots, starts, [[int(t)] for t in tokens])
-        entry.meta_dev.copy_(entry.meta_host, non_blocking=True)
-        ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max_kv,
-                          self.attn_split_keys, tiles=entry.tiles)
-        if entry.graph is None and not entry.warmed:
-            logits = self.model.forward(ctx, self.calls, None, want_all=True)
-            entry.warmed = True
-        else:
-            if entry.graph is None:
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, pool=self._graph_pool):
-                    entry.logits = self.model.forward(ctx, self.calls, None, want_all=True)
-                entry.graph = g
-            entry.graph.replay()
-            logits = entry.logits
+        words = pack_batch(slots, starts, [[int(t)] for t in tokens])
+        logits = None
+        if self.fused_decode and max(starts) + 1 <= self.fused_decode_max_context:
+            entry = self._fused.get(B)
+            if entry is None:
+                entry = self._fused[B] = _DecodeGraph(batch_layout(B, B)["_total"][0], self.device)
+                entry.plan = build_fused_plan(self, B) or False
+            if entry.plan:
+                entry.upload(words)
+                ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max(starts) + 1)
+                logits = entry.plan.run(ctx)
+                self.last_fused_ctx = ctx
+        if logits is None:
+            logits = self._decode_graph(B, words, ones, max(starts) + 1)
         self.cache.advance(slots, ones)
         if check:
             self.check_status()
         return logits
+
+    def _decode_graph(self, B, words, ones, longest) -> torch.Tensor:
+        max_kv = -(-longest // 512) * 512            # bucketed, so that the key changes rarely
+        key = (B, max_kv)
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._graphs[key] = _DecodeGraph(batch_layout(B, B)["_total"][0], self.device)
+        entry.upload(words)
+        ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max_kv,
+                          self.attn_split_keys, tiles=entry.tiles)
+        if entry.graph is None and not entry.warmed:
+            entry.warmed = True
+            return self.model.forward(ctx, self.calls, None, want_all=True)
+        if entry.graph is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self._graph_pool):
+                entry.logits = self.model.forward(ctx, self.calls, None, want_all=True)
+            entry.graph = g
+        entry.graph.replay()
+        return entry.logits
 
     # ------------------------------------------------------------------ generation
     def prefill(self, slots, prompts) -> torch.Tensor:
