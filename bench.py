@@ -34,6 +34,21 @@ LFM2_1_2B = dict(
                  "conv", "full_attention", "conv", "full_attention", "conv", "full_attention", "conv"],
     block_ff_dim=12288, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=256,
     conv_L_cache=3, conv_bias=False, rope_theta=1000000.0, norm_eps=1e-5, tie_word_embeddings=True, eos_token_id=7)
+
+
+def _lfm2(hidden, layers, attn_at, heads, ffn):
+    """An LFM2 configuration of the given sizes with the effective SwiGLU width `ffn`."""
+    d = dict(LFM2_1_2B, hidden_size=hidden, num_hidden_layers=layers, num_attention_heads=heads,
+             layer_types=["full_attention" if i in attn_at else "conv" for i in range(layers)],
+             block_ff_dim=ffn, block_auto_adjust_ff_dim=False)
+    return d
+
+
+# The secondary workloads: (configuration, batch, prompt lengths, decode steps, longest sequence)
+SECONDARY = {
+    "2.6b": (_lfm2(2048, 30, {2, 6, 10, 14, 18, 21, 24, 27}, 32, 10752), 16, (64, 4096), 256, 4096 + 512),
+    "350m": (_lfm2(1024, 16, {2, 5, 8, 10, 12, 14}, 16, 4608), 64, (1024, 32768), 128, 32768 + 256),
+}
 CONTEXT = 4096
 PROMPT_RANGE = (512, 2048)
 PREFILL_TOKENS = 2048
@@ -132,11 +147,14 @@ def print_op_trace(engine, batch: int) -> None:
     engine.status.zero_()
 
 
-def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int, trace_ops: bool = False):
-    """Prefills `batch` prompts of lengths uniform in PROMPT_RANGE, then times `steps` decode steps.
+def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int, trace_ops: bool = False,
+                prompt_range=None):
+    """Prefills `batch` prompts of lengths uniform in `prompt_range` (default PROMPT_RANGE), then times
+    `steps` decode steps.
     Returns (ms per step, total cached tokens at the middle of the timed region, launches per step)."""
     from zinfer_b200 import kernels
-    lens = rng.integers(PROMPT_RANGE[0], PROMPT_RANGE[1] + 1, size=batch).tolist()
+    lo, hi = prompt_range or PROMPT_RANGE
+    lens = rng.integers(lo, hi + 1, size=batch).tolist()
     prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
     slots = engine.start(batch)
     try:
@@ -185,6 +203,46 @@ def time_prefill(engine, torch, rng, cfg, warmup: int, num: dict, pk: dict) -> d
     flops = 2 * T * num["layer_params"] + 2 * num["head_params"] + num["n_attn"] * 2 * T * T * cfg.q_dim
     return {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
             "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+
+def secondary_arm(args) -> dict:
+    """One of the secondary workloads: unequal long prompts, then `steps` timed decode steps."""
+    import numpy as np
+    import torch
+    import zinfer_b200 as z
+    from zinfer_b200 import kernels
+
+    kernels.require_cuda()
+    pk = peaks()
+    cfg_dict, batch, prompt_range, steps, longest = SECONDARY[args.model]
+    cfg = z.config_from_dict(cfg_dict)
+    model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True)
+    rng = np.random.default_rng(0)
+    lens = np.random.default_rng(0).integers(prompt_range[0], prompt_range[1] + 1, size=batch)   # as time_decode draws them
+    page = 64
+    room = int(sum(-(-(int(n) + args.warmup + steps + 1) // page) * page for n in lens))
+    engine = z.Engine(model, max_batch=batch, max_seq_len=longest, max_tokens=room, page_size=page)
+    num = model_numbers(cfg, cfg.num_hidden_layers)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with ClockSampler() as clocks:
+        ms, cached, launches = time_decode(engine, torch, rng, batch, steps, args.warmup, cfg.vocab_size,
+                                           prompt_range=prompt_range)
+    wall = time.perf_counter() - t0
+    weight_bytes = 2 * (num["layer_params"] + num["head_params"])
+    step_bytes = weight_bytes + cached * num["kv_bytes_per_token"] + batch * num["conv_state_bytes"] * 2
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    return {"metric": f"decode tokens/s at batch {batch} (LFM2-{args.model.upper()} shape, random weights)",
+            "value": round(batch / (ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 4), "steps": steps,
+            "warmup": args.warmup, "dtype": "bf16", "impl": "zinfer_b200",
+            "config": {"model": f"LFM2-{args.model.upper()}", "global_batch": batch, "layers": cfg.num_hidden_layers,
+                       "hidden": cfg.hidden_size, "ffn": cfg.ffn_dim, "prompt_lens": f"uniform[{prompt_range[0]},{prompt_range[1]}]",
+                       "cached_tokens": int(cached), "peaks": pk["source"]},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "weight_gb": round(weight_bytes / 1e9, 3),
+                         "cache_gb": round(cached * num["kv_bytes_per_token"] / 1e9, 3)},
+            "clocks": clocks.summary(), "gpu_launches": int(launches or 0) * steps,
+            "wall_s_with_prompts": round(wall, 1)}
 
 
 def own_arm(args) -> dict:
@@ -280,6 +338,8 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only (for profiling); the JSON line then lacks the other parts")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--model", default="1.2b", choices=["1.2b"] + sorted(SECONDARY),
+                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only)")
     ap.add_argument("--trace-ops", action="store_true",
                     help="with --fused --only decode: print where block 0 of the persistent kernel spends a step")
     ap.add_argument("--fused", action="store_true", help="run decode steps of up to 16 sequences as one persistent kernel")
@@ -293,7 +353,7 @@ def main() -> int:
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: zinfer_b200 runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    print(json.dumps(own_arm(args)))
+    print(json.dumps(own_arm(args) if args.model == "1.2b" else secondary_arm(args)))
     return 0
 
 

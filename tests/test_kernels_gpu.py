@@ -500,3 +500,60 @@ def test_attention_far_key_and_window_edge(k, dtype, window):
                          i32([T - 2, T - 1]), i32([0, 1]), table2, H, Hkv, hd, scale, window, splits, keys,
                          single_token=True)
         close(o2, ref, dtype, f"single-token far key, window {window}, {splits} chunks")
+
+
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(32, 8, 64, 64, 0), (16, 8, 64, 128, 0), (6, 2, 128, 64, 0),
+                                                  (16, 1, 64, 64, 0), (3, 3, 64, 64, 0), (8, 2, 64, 64, 100),
+                                                  (5, 1, 128, 64, 70)])
+def test_single_token_attention_on_tensor_cores(k, H, Hkv, hd, page, window):
+    """The tensor-core single-token kernel against whole-sequence references: lengths around tile,
+    page and chunk edges, shuffled NaN-filled pages, one far key that must win (scaled so that
+    its score stands out), a window whose edge cuts a tile, and key chunks with empty ones."""
+    dtype = torch.bfloat16
+    assert k.attention_plan(dtype, H, Hkv, hd, page, True)[0] == "single_token_tc"
+    lens = [1, 63, 64, 65, 127, 300, 1029, 512]
+    slots = [3, 0, 5, 1, 4, 7, 2, 6]
+    scale = 1 / math.sqrt(hd)
+    setup = PagedSetup(lens, slots, 8, page, Hkv, hd, dtype, seed=5)
+    g = H // Hkv
+    qs, refs = [], []
+    for i, (L, slot) in enumerate(zip(lens, slots)):
+        kk = rnd((L, Hkv, hd), 10 + i, dtype, 0.3)
+        v = rnd((L, Hkv, hd), 30 + i, dtype)
+        q = rnd((1, H, hd), 50 + i, dtype, 0.3)
+        far = 0 if window == 0 else max(L - window, 0)        # the first key the query may see
+        if L > 3:
+            kk[far] = 0
+            kk[far, :, 0] = 12.0
+            q[:, :, 0] = 12.0
+            if window and far > 0:
+                kk[far - 1] = 0
+                kk[far - 1, :, 0] = 14.0      # one position outside the window: would win if it were seen
+        pages = torch.from_numpy(setup.table[slot, :-(-L // page)].astype(np.int64)).cuda()
+        pad = (-L) % page
+        kp = torch.cat([kk, torch.zeros(pad, Hkv, hd, dtype=dtype)]).reshape(-1, page, Hkv, hd).permute(0, 2, 1, 3)
+        vp = torch.cat([v, torch.zeros(pad, Hkv, hd, dtype=dtype)]).reshape(-1, page, Hkv, hd).permute(0, 2, 1, 3)
+        setup.k[pages] = kp.cuda()
+        setup.v[pages] = vp.cuda()
+        if pad:      # what lies behind the sequence's end in its last page must not matter
+            setup.k[pages[-1], :, page - pad:] = float("nan")
+            setup.v[pages[-1], :, page - pad:] = float("nan")
+        qs.append(q.reshape(1, H * hd))
+        refs.append(attn_ref(q.double(), kk.double(), v.double(), L - 1, window, scale).reshape(1, H * hd))
+        if L > 3:
+            won = torch.allclose(refs[-1].float().reshape(H, hd), v[far].float()[[h // g for h in range(H)]], atol=0.05)
+            assert won, "the reference itself does not pick the far key"
+    q_all, ref = torch.cat(qs).cuda(), torch.cat(refs)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    n = len(lens)
+    for splits, keys in ((1, 0), (3, 384), (9, 128), (2, 1024)):
+        out = k.attention(q_all, setup.k, setup.v, i32(list(range(n))), i32([0] * n), i32(list(range(n + 1))),
+                          i32([L - 1 for L in lens]), i32(slots), setup.table_dev, H, Hkv, hd, scale, window, splits,
+                          keys, single_token=True, kind="single_token_tc")
+        assert not torch.isnan(out.float()).any()
+        close(out, ref, dtype, f"tensor-core single-token attention, {splits} chunks of {keys}")
+    if k.attention_plan(dtype, H, Hkv, hd, 32, True)[0] == "single_token":
+        other = k.attention(q_all, setup.k, setup.v, i32(list(range(n))), i32([0] * n), i32(list(range(n + 1))),
+                            i32([L - 1 for L in lens]), i32(slots), setup.table_dev, H, Hkv, hd, scale, window, 3, 384,
+                            single_token=True, kind="single_token")
+        close(other, ref, dtype, "the one-lane-per-key kernel on the same cache")

@@ -59,6 +59,10 @@ _SIGNATURES = {
         "zk_attn_prefill_takes": "iiii",
         "zk_attn_prefill_tile_tokens": "ii",
     },
+    "attention_decode_tc": {
+        "zk_attn_decode_tc": "pppppppppiiiiiiifiip",
+        "zk_attn_decode_tc_takes": "iiii",
+    },
     "fused_decode": {
         "zk_fused_decode": "piippppp" + "ipp",
         "zk_fused_decode_op_bytes": "",
@@ -517,8 +521,10 @@ def attn_tile_shape(n_heads: int, n_kv: int) -> tuple[int, int]:
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
-    ("single_token" | "prompt_tc" | "general", tokens per tile)."""
+    ("single_token_tc" | "single_token" | "prompt_tc" | "general", tokens per tile)."""
     if dtype == torch.bfloat16 and n_heads % n_kv == 0:
+        if single_token and _fn("attention_decode_tc", "zk_attn_decode_tc_takes")(n_heads, n_kv, head_dim, page_size):
+            return "single_token_tc", 1
         if single_token and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size):
             return "single_token", 1
         if not single_token and _fn("attention_prefill", "zk_attn_prefill_takes")(n_heads, n_kv, head_dim, page_size):
@@ -532,7 +538,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     """Causal grouped-query attention of a packed batch against the paged cache.  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
-    bfloat16 kernel for that case is used when it takes the sizes.  `kind` names the kernel as
+    bfloat16 kernels for that case are used when they take the sizes.  `kind` names the kernel as
     `attention_plan` chose it (the tile table must then have that plan's tokens per tile);
     without it the general kernel or the single-token kernel runs."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
@@ -560,6 +566,18 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n_heads, n_kv, head_dim,
             page_size, window, scale, _stream()), "attention (prompt, tensor cores)")
         return out
+    if (single_token and kind in (None, "single_token_tc") and q.dtype == torch.bfloat16
+            and _fn("attention_decode_tc", "zk_attn_decode_tc_takes")(n_heads, n_kv, head_dim, page_size)):
+        _check(_fn("attention_decode_tc", "zk_attn_decode_tc")(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
+            _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
+            scale, num_splits, split_keys, _stream()), "attention (single token, tensor cores)")
+        if num_splits > 1:
+            _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
+                                                     num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+        return out
+    if kind == "single_token_tc":
+        raise KernelError("attention: the tensor-core single-token kernel does not take these sizes")
     if (single_token and kind in (None, "single_token") and q.dtype == torch.bfloat16
             and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode", "zk_attn_decode")(
