@@ -92,6 +92,84 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
   for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(sm[d]);
 }
 
+// The same for prompt steps with head sizes 64 and 128 and a rotation over the whole head in
+// half-split pairing (or none): one block per token, its warps take the head slots in turn, the
+// angles' cosines and sines are computed once per warp instead of once per head, and a lane keeps
+// its pairs (d, d + hd/2) in registers.  The arithmetic and its order are those of
+// qk_prepare_kernel, so both give the same bits.
+template <typename T, int HD>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+    qk_prepare_token_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache,
+                            T* __restrict__ v_cache, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                            const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
+                            const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+                            const int* __restrict__ page_table, int pt_stride, int H, int Hkv, float eps, int page_size,
+                            int write_kv, int* status) {
+  constexpr int E = HD / 64, HALF = HD / 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x;
+  const int slots = H + 2 * Hkv;
+  const int pos = tok_pos[t];
+  float cs[E], sn[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const float ang = inv_freq ? (float)pos * inv_freq[lane + 32 * e] : 0.f;
+    cs[e] = cosf(ang);
+    sn[e] = sinf(ang);
+  }
+  int page = -2;   // not looked up yet
+  for (int s = warp; s < (write_kv ? slots : H); s += ATT_WARPS) {
+    const int kind = s < H ? 0 : (s < H + Hkv ? 1 : 2);
+    const T* src = qkv + (size_t)t * slots * HD + (size_t)s * HD;
+    const float* w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+    float a[E], b[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      a[e] = to_f32(src[lane + 32 * e]);
+      b[e] = to_f32(src[lane + 32 * e + HALF]);
+    }
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) ss = fmaf(a[e], a[e], ss);
+#pragma unroll
+      for (int e = 0; e < E; ++e) ss = fmaf(b[e], b[e], ss);
+      ss = warp_sum(ss);
+      const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        a[e] = (a[e] * scale) * w[lane + 32 * e];
+        b[e] = (b[e] * scale) * w[lane + 32 * e + HALF];
+      }
+    }
+    if (kind != 2 && inv_freq) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float x = a[e], y = b[e];
+        a[e] = x * cs[e] - y * sn[e];
+        b[e] = x * sn[e] + y * cs[e];
+      }
+    }
+    T* dst;
+    if (kind == 0) {
+      dst = q_out + (size_t)t * H * HD + (size_t)s * HD;
+    } else {
+      if (page == -2) page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
+      if (page < 0) {
+        if (lane == 0) atomicExch(status, 2);
+        continue;
+      }
+      const int kh = kind == 1 ? s - H : s - H - Hkv;
+      dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * Hkv + kh) * page_size + pos % page_size) * HD;
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      dst[lane + 32 * e] = from_f32<T>(a[e]);
+      dst[lane + 32 * e + HALF] = from_f32<T>(b[e]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // (2) attention.  Block = (query tile, kv head x head chunk, key split).  A query tile is
 // `bq` consecutive tokens of one sequence; its rows are (token, head in group) pairs, at
@@ -350,6 +428,20 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || n_rot > hd || (n_rot & 1) || page_size <= 0) return ZK_EINVAL;
+  // many tokens, whole-head half-split rotation (or none): one block per token
+  if (n_tokens >= 64 && !dense_out && (hd == 64 || hd == 128) && (!inv_freq || (n_rot == hd && !interleaved)) &&
+      (dtype == ZK_F32 || dtype == ZK_BF16)) {
+#define ZK_QKP(T, HDV)                                                                                               \
+  qk_prepare_token_kernel<T, HDV><<<n_tokens, ATT_WARPS * 32, 0, stream>>>(                                          \
+      (const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, \
+      pt_stride, H, Hkv, eps, page_size, write_kv, status)
+    if (dtype == ZK_F32 && hd == 64) ZK_QKP(float, 64);
+    else if (dtype == ZK_F32) ZK_QKP(float, 128);
+    else if (hd == 64) ZK_QKP(bf16, 64);
+    else ZK_QKP(bf16, 128);
+#undef ZK_QKP
+    return ZK_LAUNCH_STATUS();
+  }
   const long long items = (long long)n_tokens * (H + 2 * Hkv);
   const int blocks = (int)((items + ATT_WARPS - 1) / ATT_WARPS);
   if (dtype == ZK_F32)

@@ -9,6 +9,7 @@
 // tokens and only reads the state; `conv_state_update` then writes the new state.  For a
 // step of single tokens `conv_decode` does both at once.
 #include "common.cuh"
+#include <stdint.h>
 
 // Column of part p (0 = B, 1 = C, 2 = X) of channel ch in a bcx row: three blocks of D columns
 // (il = 0), or groups of il channels laid out as [B (il) | C (il) | X (il)] (il > 0, the layout
@@ -44,6 +45,65 @@ __global__ void conv_forward_kernel(const T* __restrict__ bcx, const float* __re
   }
   if (bias) acc += bias[ch];
   y[(size_t)t * D + ch] = from_f32<T>(to_f32(bcx[(size_t)t * 3 * D + bcx_col(1, ch, D, il)]) * acc);
+}
+
+// The same for bfloat16 with one thread per (token, 8 adjacent channels): 16-byte loads and
+// stores.  D and il are multiples of 8, so the 8 channels are adjacent in every part of a row.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float f[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(p[i]);
+    f[2 * i + 1] = __high2float(p[i]);
+  }
+}
+
+__global__ void conv_forward_vec8_kernel(const bf16* __restrict__ bcx, const float* __restrict__ state,
+                                         const float* __restrict__ w, const float* __restrict__ bias,
+                                         const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                                         const int* __restrict__ seq_slot, bf16* __restrict__ y, int n_tokens, int D,
+                                         int K, long long state_slot_stride, int il) {
+  const int ch = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  const int t = blockIdx.x;
+  if (ch >= D || t >= n_tokens) return;
+  const int b = tok_seq[t];
+  const int i = t - cu_q[b];
+  const float* st = state + (size_t)seq_slot[b] * state_slot_stride;
+  const size_t cb = bcx_col(0, ch, D, il), cc = bcx_col(1, ch, D, il), cx = bcx_col(2, ch, D, il);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int j = i - (K - 1) + k;
+    float u[8];
+    if (j >= 0) {
+      const bf16* row = bcx + (size_t)(t - (i - j)) * 3 * D;
+      float bv[8], xv[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(row + cb), bv);
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(row + cx), xv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) u[e] = bv[e] * xv[e];
+    } else {
+      const float4* sp = reinterpret_cast<const float4*>(st + (size_t)(K - 1 + j) * D + ch);
+      const float4 a = sp[0], c = sp[1];
+      u[0] = a.x, u[1] = a.y, u[2] = a.z, u[3] = a.w, u[4] = c.x, u[5] = c.y, u[6] = c.z, u[7] = c.w;
+    }
+    const float4* wp = reinterpret_cast<const float4*>(w + (size_t)k * D + ch);
+    const float4 wa = wp[0], wc = wp[1];
+    const float wk[8] = {wa.x, wa.y, wa.z, wa.w, wc.x, wc.y, wc.z, wc.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[e], u[e], acc[e]);
+  }
+  float cv[8];
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(bcx + (size_t)t * 3 * D + cc), cv);
+  __nv_bfloat162 o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float b0 = bias ? bias[ch + 2 * e] : 0.f, b1 = bias ? bias[ch + 2 * e + 1] : 0.f;
+    o[e] = __floats2bfloat162_rn(cv[2 * e] * (bias ? acc[2 * e] + b0 : acc[2 * e]),
+                                 cv[2 * e + 1] * (bias ? acc[2 * e + 1] + b1 : acc[2 * e + 1]));
+  }
+  *reinterpret_cast<uint4*>(y + (size_t)t * D + ch) = *reinterpret_cast<const uint4*>(o);
 }
 
 // One thread per (sequence, channel): state <- last K-1 values of u, older state rows survive
@@ -107,6 +167,14 @@ int zk_conv_forward(const void* bcx, const float* state, const float* w, const f
   if (n_tokens <= 0) return 0;
   if (D <= 0 || K < 2 || il < 0 || (il > 0 && D % il)) return ZK_EINVAL;
   const int threads = 128;
+  if (dtype == ZK_BF16 && D % 8 == 0 && il % 8 == 0 && state_slot_stride % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(bcx) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(state) |
+       reinterpret_cast<uintptr_t>(w)) % 16 == 0) {
+    dim3 grid8(n_tokens, ceil_div_i(D / 8, threads));
+    conv_forward_vec8_kernel<<<grid8, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
+                                                            (bf16*)y, n_tokens, D, K, state_slot_stride, il);
+    return ZK_LAUNCH_STATUS();
+  }
   dim3 grid(n_tokens, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
     conv_forward_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
