@@ -342,6 +342,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 }
 
 // (3) merge: out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s.  One warp per (token, head).
+// A lane holds the (m, l) of one chunk (32 chunks at a time), so that the loads of all chunks are
+// under way together; the sums run over the chunks in ascending order whatever the timing.
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   T* __restrict__ out, int n_rows, int hd, int num_splits) {
@@ -349,21 +351,46 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   float M = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[((size_t)s * n_rows + row) * 2]);
+  for (int s0 = 0; s0 < num_splits; s0 += 32) {
+    const int s = s0 + lane;
+    const float ms = s < num_splits ? part_ml[((size_t)s * n_rows + row) * 2] : -INFINITY;
+    M = fmaxf(M, warp_max(ms));
+  }
   float L = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float ms = part_ml[((size_t)s * n_rows + row) * 2];
-    if (ms != -INFINITY) L += expf(ms - M) * part_ml[((size_t)s * n_rows + row) * 2 + 1];
+  float acc[8];   // head sizes up to 256: 8 values per lane
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int s0 = 0; s0 < num_splits; s0 += 32) {
+    const int s = s0 + lane;
+    float ms = -INFINITY, ls = 0.f;
+    if (s < num_splits) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)s * n_rows + row) * 2);
+      ms = ml.x;
+      ls = ml.y;
+    }
+    const float e = ms == -INFINITY ? 0.f : expf(ms - M);
+    const int n_here = min(32, num_splits - s0);
+    for (int j = 0; j < n_here; ++j) L = fmaf(__shfl_sync(0xffffffffu, e, j), __shfl_sync(0xffffffffu, ls, j), L);
+    for (int j0 = 0; j0 < n_here; j0 += 8) {
+      float v[8][8], w[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int j = j0 + u;
+        w[u] = j < n_here ? __shfl_sync(0xffffffffu, e, j & 31) : 0.f;
+        const float* po = part_o + ((size_t)(s0 + j) * n_rows + row) * hd;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[u][i] = (w[u] != 0.f && lane + 32 * i < hd) ? po[lane + 32 * i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[u], v[u][i], acc[i]);
+    }
   }
   const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int d = lane; d < hd; d += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ms = part_ml[((size_t)s * n_rows + row) * 2];
-      if (ms != -INFINITY) acc = fmaf(expf(ms - M), part_o[((size_t)s * n_rows + row) * hd + d], acc);
-    }
-    out[(size_t)row * hd + d] = from_f32<T>(acc * inv);
-  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (lane + 32 * i < hd) out[(size_t)row * hd + lane + 32 * i] = from_f32<T>(acc[i] * inv);
 }
 
 namespace {
