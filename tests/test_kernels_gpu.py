@@ -557,3 +557,15 @@ def test_single_token_attention_on_tensor_cores(k, H, Hkv, hd, page, window):
                             i32([L - 1 for L in lens]), i32(slots), setup.table_dev, H, Hkv, hd, scale, window, 3, 384,
                             single_token=True, kind="single_token")
         close(other, ref, dtype, "the one-lane-per-key kernel on the same cache")
+
+
+def test_size_predicates_known_to_python_agree_with_the_libraries(k):
+    """`kernels._may_take` lets a model skip compiling a library that cannot serve it; it must never
+    say no where the library says yes."""
+    libs = {"attention_decode": "zk_attn_decode_takes", "attention_decode_tc": "zk_attn_decode_tc_takes",
+            "attention_prefill": "zk_attn_prefill_takes"}
+    for lib, fn in libs.items():
+        for H, Hkv in ((4, 2), (3, 1), (32, 8), (16, 1), (24, 1), (9, 1), (5, 5)):
+            for hd in (16, 32, 48, 64, 80, 96, 128, 256):
+                for page in (16, 32, 64, 96, 128):
+                    assert bool(k._fn(lib, fn)(H, Hkv, hd, page)) == k._may_take(lib, H, Hkv, hd, page), (lib, H, Hkv, hd, page)

@@ -518,16 +518,33 @@ def attn_tile_shape(n_heads: int, n_kv: int) -> tuple[int, int]:
     return max(1, rows // gc), gc
 
 
+def _may_take(lib: str, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    """The sizes a specialised attention library can take at all, known here so that a model it
+    cannot serve never has it compiled; the library's own `*_takes` has the last word."""
+    group = n_heads // n_kv
+    if lib == "attention_decode":
+        return head_dim in (32, 64, 96, 128) and group <= 8 and page_size % 32 == 0
+    if lib == "attention_decode_tc":
+        return head_dim in (64, 128) and group <= 16 and page_size % 64 == 0
+    if lib == "attention_prefill":
+        return head_dim in (64, 128) and page_size % 64 == 0
+    raise KeyError(lib)
+
+
+def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    return _may_take(lib, n_heads, n_kv, head_dim, page_size) and bool(_fn(lib, fn)(n_heads, n_kv, head_dim, page_size))
+
+
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
     ("single_token_tc" | "single_token" | "prompt_tc" | "general", tokens per tile)."""
     if dtype == torch.bfloat16 and n_heads % n_kv == 0:
-        if single_token and _fn("attention_decode_tc", "zk_attn_decode_tc_takes")(n_heads, n_kv, head_dim, page_size):
+        if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token_tc", 1
-        if single_token and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size):
+        if single_token and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token", 1
-        if not single_token and _fn("attention_prefill", "zk_attn_prefill_takes")(n_heads, n_kv, head_dim, page_size):
+        if not single_token and _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim, page_size):
             return "prompt_tc", _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_kv)
     return "general", attn_tile_shape(n_heads, n_kv)[0]
 
@@ -558,8 +575,8 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         part_o = torch.empty((num_splits, n * n_heads, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
     if kind == "prompt_tc":
-        if q.dtype != torch.bfloat16 or not _fn("attention_prefill", "zk_attn_prefill_takes")(n_heads, n_kv, head_dim,
-                                                                                            page_size):
+        if q.dtype != torch.bfloat16 or not _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim,
+                                                   page_size):
             raise KernelError("attention: the tensor-core prompt kernel does not take these sizes")
         _check(_fn("attention_prefill", "zk_attn_prefill")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
@@ -567,7 +584,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             page_size, window, scale, _stream()), "attention (prompt, tensor cores)")
         return out
     if (single_token and kind in (None, "single_token_tc") and q.dtype == torch.bfloat16
-            and _fn("attention_decode_tc", "zk_attn_decode_tc_takes")(n_heads, n_kv, head_dim, page_size)):
+            and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode_tc", "zk_attn_decode_tc")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
             _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
@@ -579,7 +596,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if kind == "single_token_tc":
         raise KernelError("attention: the tensor-core single-token kernel does not take these sizes")
     if (single_token and kind in (None, "single_token") and q.dtype == torch.bfloat16
-            and _fn("attention_decode", "zk_attn_decode_takes")(n_heads, n_kv, head_dim, page_size)):
+            and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode", "zk_attn_decode")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
             _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
