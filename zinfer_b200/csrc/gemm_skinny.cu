@@ -20,6 +20,7 @@
 //  * EPI_CONV: the block owns rows ch, D + ch, 2D + ch of the short convolution's in_proj and
 //    runs the gated convolution with its state update on them (src/model.zig:2002-2020).
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace {
 
@@ -79,7 +80,13 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int M = a.M, N = a.N, K = a.K;
-  const int n0 = blockIdx.x * (EPI == EPI_PLAIN ? 16 * RG : 16);
+  // A block takes the tasks blockIdx.x, blockIdx.x + gridDim.x, ...: a task is 16 * RG output
+  // columns (EPI_PLAIN) or 16 (fused epilogues).  With as many blocks as tasks that is one each;
+  // fewer blocks are launched where a prologue (the norm) should be paid once for several tasks.
+  constexpr int TASK_COLS = EPI == EPI_PLAIN ? 16 * RG : 16;
+  const int n_tasks = (N + TASK_COLS - 1) / TASK_COLS;
+  int task = blockIdx.x;
+  int n0 = task * TASK_COLS;
 
   const int slabs = (K + 31) / 32;
   const int per = (slabs + WARPS - 1) / WARPS;
@@ -87,19 +94,23 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
 
   const bf16* wrow[RG][2];
   bool wok[RG][2];
+  auto set_task = [&]() {
+    n0 = task * TASK_COLS;
 #pragma unroll
-  for (int r = 0; r < RG; ++r)
+    for (int r = 0; r < RG; ++r)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      // EPI_PLAIN: weight row = output column.  Fused epilogues: the weights are stored in groups of
-      // 16 rows per part (16 gate rows, their 16 up rows; 16 B, 16 C, 16 X rows), so the RG groups of
-      // a block are RG * 16 adjacent rows and stream like any 16 * RG rows.
-      const int col = n0 + (EPI == EPI_PLAIN ? r * 16 : 0) + g + 8 * h;
-      wok[r][h] = col < N;
-      const size_t row = EPI == EPI_PLAIN ? (size_t)(wok[r][h] ? col : 0)
-                                          : (size_t)blockIdx.x * (16 * RG) + r * 16 + (wok[r][h] ? g + 8 * h : 0);
-      wrow[r][h] = a.W + row * a.ldw;
-    }
+      for (int h = 0; h < 2; ++h) {
+        // EPI_PLAIN: weight row = output column.  Fused epilogues: the weights are stored in groups of
+        // 16 rows per part (16 gate rows, their 16 up rows; 16 B, 16 C, 16 X rows), so the RG groups of
+        // a task are RG * 16 adjacent rows and stream like any 16 * RG rows.
+        const int col = n0 + (EPI == EPI_PLAIN ? r * 16 : 0) + g + 8 * h;
+        wok[r][h] = col < N;
+        const size_t row = EPI == EPI_PLAIN ? (size_t)(wok[r][h] ? col : 0)
+                                            : (size_t)task * (16 * RG) + r * 16 + (wok[r][h] ? g + 8 * h : 0);
+        wrow[r][h] = a.W + row * a.ldw;
+      }
+  };
+  set_task();
   const uint4 zero = make_uint4(0, 0, 0, 0);
 
   uint4 wv[UNROLL][RG][2];
@@ -169,6 +180,11 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     __syncthreads();
   }
 
+  bool xok[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) xok[t] = t * 8 + g < M;
+
+  for (;;) {   // the block's tasks
   float acc[RG][NT][4];
 #pragma unroll
   for (int r = 0; r < RG; ++r)
@@ -176,10 +192,6 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     for (int t = 0; t < NT; ++t)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[r][t][i] = 0.f;
-
-  bool xok[NT];
-#pragma unroll
-  for (int t = 0; t < NT; ++t) xok[t] = t * 8 + g < M;
 
   for (int s = s_begin; s < s_end; s += UNROLL) {
     if (!PIPE) load_w(s);
@@ -266,7 +278,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
       if (m >= M || ch >= N) continue;
       float bv = total(i, m), cv = total(16 + i, m), xval = total(32 + i, m);
       if (a.bias) {  // stored in the weights' row order
-        const size_t base = (size_t)blockIdx.x * 48 + i;
+        const size_t base = (size_t)task * 48 + i;
         bv += a.bias[base];
         cv += a.bias[base + 16];
         xval += a.bias[base + 32];
@@ -286,7 +298,18 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
       C[(size_t)m * a.ldc + ch] = __float2bfloat16_rn(round_bf16(cv) * sum);
     }
   }
+  task += gridDim.x;
+  if (task >= n_tasks) break;
+  __syncthreads();   // the epilogue has read `red`
+  set_task();
+  if (PIPE) load_w(s_begin);
+  }
 }
+
+// Most blocks of a kernel with the norm prologue: two per SM.  Measured on the LFM2-1.2B shapes at
+// one row (where every contraction takes the norm itself): 0.698 ms a step with 296 blocks, 0.771
+// with 148, 0.730 with 444, 0.779 with one block per task.
+int norm_grid_cap() { return 148 * 2; }
 
 template <int WARPS, int RG, int NT>
 size_t smem_bytes(bool norm, int K) {
@@ -304,7 +327,8 @@ int launch(const Args& a, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const int grid = ceil_div_i(a.N, EPI == EPI_PLAIN ? 16 * RG : 16);
+  int grid = ceil_div_i(a.N, EPI == EPI_PLAIN ? 16 * RG : 16);
+  if (NORM && grid > norm_grid_cap()) grid = norm_grid_cap();   // the norm prologue once for several tasks
   kern<<<grid, WARPS * 32, smem, stream>>>(a);
   return ZK_LAUNCH_STATUS();
 }
