@@ -190,8 +190,10 @@ def test_gemm_skinny_swiglu(k, M, F, K, norm):
         k.gemm_skinny_swiglu(inp, w_mixed[:48])        # 24 outputs: not whole groups of 16
 
 
-@pytest.mark.parametrize("M,F,K", [(65, 64, 64), (300, 8192, 2048), (130, 208, 520)])
+@pytest.mark.parametrize("M,F,K", [(65, 64, 64), (300, 8192, 2048), (130, 208, 520), (64, 8192, 2048), (17, 208, 520),
+                                   (40, 64, 64), (1, 32, 64)])
 def test_gemm_tc_with_swiglu_epilogue(k, M, F, K):
+    """Normal mode (more than 64 rows) and swapped mode (the weights on the 128-row side, K whole)."""
     a = rnd((M, K), 1, torch.bfloat16).cuda()
     halves = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
     g, u = a.double() @ halves[:F].double().T, a.double() @ halves[F:].double().T

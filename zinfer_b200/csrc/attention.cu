@@ -456,7 +456,7 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || n_rot > hd || (n_rot & 1) || page_size <= 0) return ZK_EINVAL;
   // many tokens, whole-head half-split rotation (or none): one block per token
-  if (n_tokens >= 64 && !dense_out && (hd == 64 || hd == 128) && (!inv_freq || (n_rot == hd && !interleaved)) &&
+  if (n_tokens >= 256 && !dense_out && (hd == 64 || hd == 128) && (!inv_freq || (n_rot == hd && !interleaved)) &&
       (dtype == ZK_F32 || dtype == ZK_BF16)) {
 #define ZK_QKP(T, HDV)                                                                                               \
   qk_prepare_token_kernel<T, HDV><<<n_tokens, ATT_WARPS * 32, 0, stream>>>(                                          \

@@ -341,6 +341,16 @@ __global__ void __launch_bounds__(THREADS)
         if (p.splits > 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = v[j];
+        } else if (p.swiglu) {
+          // a warp's 32 rows are 16 gate rows and their 16 up rows (N is a multiple of 32, so the
+          // whole warp is on one side of N): lane l < 16 takes the up value of lane l + 16
+          const int f = (n >> 5) * 16 + (n & 15);   // output column of this gate row
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
+            if ((lane & 16) == 0 && n < p.N && c0 + j < p.M)
+              C[(size_t)(c0 + j) * p.ldc + f] = from_f32<TC>(v[j] / (1.0f + expf(-v[j])) * up);
+          }
         } else if (n < p.N) {
           const float b = p.bias ? p.bias[n] : 0.f;
           float old[16];
@@ -451,13 +461,13 @@ extern "C" {
 // X [M, K], W [N, K] bfloat16, K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
 // M <= 64 runs swapped (weights on the 128-row side) with K cut into `splits` parts (rounded down
 // to 1, 2, 4 or 8: a cluster's size); larger M runs normal and ignores splits.  With `swiglu`
-// (normal mode only) W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2]
+// (not with split K) W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2]
 // receives silu(gate) * up (src/model.zig:1085-1117).
 int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
                int out_dtype, int accumulate, int splits, int swiglu, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < (swiglu ? N / 2 : N) || !status) return ZK_EINVAL;
-  if (swiglu && (M <= 64 || N % 32 || bias || accumulate)) return ZK_EINVAL;
+  if (swiglu && (N % 32 || bias || accumulate || (M <= 64 && splits > 1))) return ZK_EINVAL;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
   if (out_dtype != ZK_F32 && out_dtype != ZK_BF16) return ZK_EINVAL;
   Params p{};

@@ -271,16 +271,15 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
     More than 64 rows: 128 x 128 tiles of tokens x weight rows.  Up to 64 rows: the weights take
     the 128-row side and K is cut into `splits` (1, 2, 4 or 8) parts, one per block of a cluster,
-    that are added in order.  With `swiglu` (more
-    than 64 rows) w holds groups of 16 gate rows and their 16 up rows and the result is
-    silu(gate) * up, [M, N/2]."""
+    that are added in order.  With `swiglu` (not with split K) w holds groups of 16 gate rows and
+    their 16 up rows and the result is silu(gate) * up, [M, N/2]."""
     if not gemm_tc_takes(a, w, out):
         raise KernelError(f"gemm_tc: a {tuple(a.shape)} / w {tuple(w.shape)} need bfloat16, K a multiple of 8 and "
                           "16-byte aligned rows")
     M, K = a.shape
     N = w.shape[0]
-    if swiglu and (M <= 64 or N % 32 or accumulate or bias is not None):
-        raise KernelError("gemm_tc: the SwiGLU epilogue needs more than 64 rows, N a multiple of 32, no bias")
+    if swiglu and ((M <= 64 and splits > 1) or N % 32 or accumulate or bias is not None):
+        raise KernelError("gemm_tc: the SwiGLU epilogue needs unsplit K, N a multiple of 32, no bias")
     n_out = N // 2 if swiglu else N
     if out is None:
         if accumulate:

@@ -9,6 +9,7 @@ import torch
 from .. import kernels
 from .base import FEED_FORWARDS, FeedForward, WeightSpec
 from .linear import FUSION_GROUP, as_tensor, fused_input, interleave_rows, linear
+from .linear_bf16 import TC_SWAPPED_MIN_ROWS, swapped_splits
 
 
 class SwiGLU(FeedForward):
@@ -40,8 +41,11 @@ class SwiGLU(FeedForward):
                 h = kernels.gemm_skinny_swiglu(x, w)
             else:
                 x = as_tensor(xn)
-                if x.shape[0] > kernels.gemm_skinny_max_m() and kernels.gemm_tc_takes(x, w):
-                    h = kernels.gemm_tc(x, w, swiglu=True)       # prompt steps: activation in the epilogue
+                rows = x.shape[0]
+                # prompt steps, and steps of 17..64 rows whose K is not split: activation in the epilogue
+                if (rows > kernels.gemm_skinny_max_m() or (rows >= TC_SWAPPED_MIN_ROWS and swapped_splits(w.shape[0]) == 1)) \
+                        and kernels.gemm_tc_takes(x, w):
+                    h = kernels.gemm_tc(x, w, swiglu=True)
         if h is None:
             h = kernels.silu_mul(linear(xn, w), self.interleave)
         linear(h, self.w_down, out=out, accumulate=accumulate)
