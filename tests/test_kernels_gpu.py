@@ -118,8 +118,10 @@ def test_gemm_skinny(k, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 331 * 8, 2048), (2048, 6144, 2048), (130, 264, 8200),
-                                   (65, 16, 72), (300, 2048, 8192)])
+                                   (65, 16, 72), (300, 2048, 8192), (2500, 4096, 128), (4200, 2304, 192)])
 def test_gemm_tc_prompt_shapes(k, M, N, K):
+    """One tile per block, and (many tiles, N a multiple of 256: the last three) persistent blocks with
+    128 x 256 tiles; row tails, K tails, every way of storing."""
     a = rnd((M, K), 5, torch.bfloat16).cuda()
     w = rnd((N, K), 6, torch.bfloat16, 0.1).cuda()
     bias = rnd((N,), 7, torch.float32).cuda()
@@ -191,7 +193,7 @@ def test_gemm_skinny_swiglu(k, M, F, K, norm):
 
 
 @pytest.mark.parametrize("M,F,K", [(65, 64, 64), (300, 8192, 2048), (130, 208, 520), (64, 8192, 2048), (17, 208, 520),
-                                   (40, 64, 64), (1, 32, 64)])
+                                   (40, 64, 64), (1, 32, 64), (700, 8192, 256), (2100, 2304, 96)])
 def test_gemm_tc_with_swiglu_epilogue(k, M, F, K):
     """Normal mode (more than 64 rows) and swapped mode (the weights on the 128-row side, K whole)."""
     a = rnd((M, K), 1, torch.bfloat16).cuda()
