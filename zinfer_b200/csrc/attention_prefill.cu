@@ -73,7 +73,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
   const int g = lane >> 2, c = lane & 3;
   const int G = H / Hkv, chunks = G / GP;
   const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
-  const int b = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
+  // tiles are taken from the last (a sequence's late tokens see the most keys) to the first, so
+  // that the long blocks start first and the short ones fill the tail
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int t_base = cu_q[b], Tq = cu_q[b + 1] - t_base;
   const int start = seq_start[b];
   const int* pt = page_table + (size_t)seq_slot[b] * pt_stride;

@@ -166,15 +166,25 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
       row_scale[threadIdx.x] = 1.0f / sqrtf(t / (float)K + a.eps);
     }
     __syncthreads();
-    for (int m = 0; m < M; ++m) {
-      const float sc = row_scale[m];
-      for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
-        const float4 v = *reinterpret_cast<const float4*>(a.Xf + (size_t)m * a.ldx + k);
-        const float4 w = *reinterpret_cast<const float4*>(a.norm_w + k);
-        uint2 pk;
-        pk.x = pack2((v.x * sc) * w.x, (v.y * sc) * w.y);
-        pk.y = pack2((v.z * sc) * w.z, (v.w * sc) * w.w);
-        *reinterpret_cast<uint2*>(xs + (size_t)m * xs_ld + k) = pk;
+    // second pass: the rows again (from L2), four at a time so that their loads are under way together
+    for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
+      const float4 w = *reinterpret_cast<const float4*>(a.norm_w + k);
+      for (int m0 = 0; m0 < M; m0 += 4) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          v[j] = (m0 + j < M) ? *reinterpret_cast<const float4*>(a.Xf + (size_t)(m0 + j) * a.ldx + k)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (m0 + j < M) {
+            const float sc = row_scale[m0 + j];
+            uint2 pk;
+            pk.x = pack2((v[j].x * sc) * w.x, (v[j].y * sc) * w.y);
+            pk.y = pack2((v[j].z * sc) * w.z, (v[j].w * sc) * w.w);
+            *reinterpret_cast<uint2*>(xs + (size_t)(m0 + j) * xs_ld + k) = pk;
+          }
+        }
       }
     }
     __syncthreads();
