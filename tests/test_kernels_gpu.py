@@ -236,8 +236,8 @@ def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
     """A row's contraction is the same bits alone, in a batch, and at another place of it, as long
-    as the same kernel runs: in float32 always; in bfloat16 among batches of up to 16 rows (the
-    mma.sync kernel) and among batches of 17 to 64 rows (the tcgen05 kernel with split K)."""
+    as the same kernel runs: in float32 always; in bfloat16 among batches of up to 8 rows (the
+    mma.sync kernel) and among batches of 9 to 64 rows (the tcgen05 kernel with split K)."""
     from zinfer_b200.parts.linear import linear
     a = rnd((70, 96), 9, dtype).cuda()
     w = rnd((200, 96), 10, dtype, 0.1).cuda()
@@ -247,14 +247,15 @@ def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
         moved = linear(a[30:40].contiguous(), w, out_dtype=torch.float32)
         assert torch.equal(full[33], one[0]) and torch.equal(full[33], moved[3])
         return
-    small = linear(a[20:36].contiguous(), w, out_dtype=torch.float32)            # 16 rows
+    small = linear(a[28:36].contiguous(), w, out_dtype=torch.float32)            # 8 rows
     one = linear(a[33:34].contiguous(), w, out_dtype=torch.float32)
-    moved = linear(a[30:40].contiguous(), w, out_dtype=torch.float32)
-    assert torch.equal(small[13], one[0]) and torch.equal(small[13], moved[3])
+    moved = linear(a[30:35].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(small[5], one[0]) and torch.equal(small[5], moved[3])
     wide = rnd((2048, 96), 11, dtype, 0.1).cuda()                               # enough rows for a split of K
     big = linear(a[:64].contiguous(), wide, out_dtype=torch.float32)
     mid = linear(a[20:40].contiguous(), wide, out_dtype=torch.float32)          # 20 rows
-    assert torch.equal(big[33], mid[13])
+    few = linear(a[30:39].contiguous(), wide, out_dtype=torch.float32)          # 9 rows
+    assert torch.equal(big[33], mid[13]) and torch.equal(big[33], few[3])
 
 
 # ------------------------------------------------------------------------------- short convolution

@@ -9,12 +9,13 @@ from __future__ import annotations
 from .. import kernels
 
 
-# Between 17 and 64 rows the tcgen05 kernel with the weights on its 128-row side beats the mma.sync
+# Between 9 and 64 rows the tcgen05 kernel with the weights on its 128-row side beats the mma.sync
 # kernel (measured at 64 rows on the LFM2-1.2B shapes: 18 us against 44 us for N = 16384, 13 against
-# 22 for N = 6144, 9 against 12 for N = 2048, 14 against 38 for N = 2048 with K = 8192); up to 8 rows
-# the mma.sync kernel is as fast or faster.  K is split over a cluster when the weight matrix alone
+# 22 for N = 6144, 9 against 12 for N = 2048, 14 against 38 for N = 2048 with K = 8192; a whole step
+# of 9 sequences 0.97 against 1.13 ms, of 16 sequences 1.15 against 1.31 ms); up to 8 rows the
+# mma.sync kernel is as fast or faster.  K is split over a cluster when the weight matrix alone
 # gives fewer 128-row tiles than there are SMs.
-TC_SWAPPED_MIN_ROWS = 17
+TC_SWAPPED_MIN_ROWS = 9
 
 
 def swapped_splits(n_weight_rows: int) -> int:
