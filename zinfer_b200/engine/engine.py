@@ -55,8 +55,9 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
 
-    def upload(self, words) -> None:
-        """Copies the packed batch description to the static device buffer."""
+    def upload(self, words, dev_tokens: Optional[torch.Tensor] = None) -> None:
+        """Copies the packed batch description to the static device buffer; `dev_tokens`, if
+        given, then replaces its token ids (the first array of the description) on the device."""
         i = self._next
         self._next = (i + 1) % self.RING
         if self._copied[i] is not None:
@@ -66,6 +67,21 @@ class _DecodeGraph:
         if self._copied[i] is None:
             self._copied[i] = torch.cuda.Event()
         self._copied[i].record()
+        if dev_tokens is not None:
+            self.meta_dev[:dev_tokens.numel()].copy_(dev_tokens)
+
+
+class _PendingTokens:
+    def __init__(self, engine, host, done):
+        self.engine, self.host, self.done = engine, host, done
+
+    def wait(self) -> list[int]:
+        self.done.synchronize()
+        both = self.host.tolist()
+        if both[-1]:
+            self.engine.status.zero_()
+            raise StepError(_STATUS_TEXT.get(both[-1], f"device status {both[-1]}"))
+        return both[:-1]
 
 
 class Engine:
@@ -206,19 +222,30 @@ class Engine:
         return self.model.forward(ctx, self.calls, want_rows)
 
     # ------------------------------------------------------------------ single-token steps
-    def decode(self, slots: Sequence[int], tokens: Sequence[int], check: bool = False) -> torch.Tensor:
+    supports_device_tokens = True   # `decode` takes the tokens as an int32 tensor on the device too
+
+    def decode(self, slots: Sequence[int], tokens, check: bool = False) -> torch.Tensor:
         """One token for each sequence, logits [len(slots), vocab] for all of them.  The same
         computation as `step(slots, [[t] for t in tokens])`, replayed from a CUDA graph: a step of
         single tokens is some hundred small kernels, and launching them one by one costs more than
         running them.  One graph per (batch size, key-chunk layout); its first use runs
         eagerly (which also loads every kernel), its second use is captured.  With
         `fused_decode` the step is one launch of the persistent kernel instead.  The returned
-        tensor is a static output buffer: use it before the next call."""
+        tensor is a static output buffer: use it before the next call.  `tokens` is a sequence of
+        ints, or an int32 tensor [len(slots)] on the device (a sampler's output): the step then
+        starts without the host having seen them."""
+        on_device = isinstance(tokens, torch.Tensor)
         if not self.use_graphs:
-            return self.step(slots, [[int(t)] for t in tokens], check=check)
+            host = tokens.cpu().tolist() if on_device else tokens
+            return self.step(slots, [[int(t)] for t in host], check=check)
         B = len(slots)
         if B != len(tokens) or len(set(slots)) != B:
             raise ValueError("one token per distinct slot")
+        dev_tokens = None
+        if on_device:
+            if tokens.dtype != torch.int32 or not tokens.is_cuda or tokens.dim() != 1:
+                raise ValueError("device tokens must be a one-dimensional int32 CUDA tensor")
+            dev_tokens, tokens = tokens, [0] * B
         ones = [1] * B
         self.cache.reserve(slots, ones)
         self.cache.sync()
@@ -231,24 +258,24 @@ class Engine:
                 entry = self._fused[B] = _DecodeGraph(batch_layout(B, B)["_total"][0], self.device)
                 entry.plan = build_fused_plan(self, B) or False
             if entry.plan:
-                entry.upload(words)
+                entry.upload(words, dev_tokens)
                 ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max(starts) + 1)
                 logits = entry.plan.run(ctx)
                 self.last_fused_ctx = ctx
         if logits is None:
-            logits = self._decode_graph(B, words, ones, max(starts) + 1)
+            logits = self._decode_graph(B, words, ones, max(starts) + 1, dev_tokens)
         self.cache.advance(slots, ones)
         if check:
             self.check_status()
         return logits
 
-    def _decode_graph(self, B, words, ones, longest) -> torch.Tensor:
+    def _decode_graph(self, B, words, ones, longest, dev_tokens=None) -> torch.Tensor:
         max_kv = -(-longest // 512) * 512            # bucketed, so that the key changes rarely
         key = (B, max_kv)
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._graphs[key] = _DecodeGraph(batch_layout(B, B)["_total"][0], self.device)
-        entry.upload(words)
+        entry.upload(words, dev_tokens)
         ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max_kv,
                           self.attn_split_keys, tiles=entry.tiles)
         if entry.graph is None and not entry.warmed:
@@ -274,6 +301,16 @@ class Engine:
             self.status.zero_()
             raise StepError(_STATUS_TEXT.get(both[-1], f"device status {both[-1]}"))
         return both[:-1]
+
+    def read_tokens_async(self, tokens: torch.Tensor):
+        """Starts copying sampled tokens (and the status word) to the host; the returned object's
+        `wait()` gives them once the copy has run, whatever was launched after it."""
+        both = torch.cat([tokens.to(torch.int32), self.status])
+        host = torch.empty(both.shape, dtype=torch.int32, pin_memory=True)
+        host.copy_(both, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return _PendingTokens(self, host, done)
 
     def generate(self, prompts, max_new_tokens: int = 256, sampling=None, stop_ids=None, on_step=None,
                  **sampling_options):

@@ -14,6 +14,8 @@ The loop talks to a backend with five methods (`start`, `finish`, `prefill`, `de
 from __future__ import annotations
 
 import time
+
+import torch
 from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
 
@@ -117,11 +119,18 @@ class GenerationLoop:
                     sampler.accept(r, prompts[r])
                 t0 = time.perf_counter()
                 logits = be.prefill([slot_of[r] for r in batch], [list(prompts[r]) for r in batch])
-                toks = be.read_tokens(sampler.sample(logits, batch))
+                toks_dev = sampler.sample(logits, batch)
+                toks = be.read_tokens(toks_dev)
                 self.stats.t_prompt_s += time.perf_counter() - t0
                 self.stats.n_prompt += sum(lens[r] for r in batch)
                 active = list(batch)
                 t0 = time.perf_counter()
+                if (getattr(be, "supports_device_tokens", False) and not getattr(sampler, "needs_history", True)
+                        and isinstance(toks_dev, torch.Tensor)):
+                    self._run_ahead(be, sampler, active, toks, toks_dev, slot_of, out, results, lens, budgets, reasons,
+                                    stop, on_step)
+                    self.stats.t_gen_s += time.perf_counter() - t0
+                    continue
                 while True:
                     live, feed, emitted = [], [], {}
                     for r, tok in zip(active, toks):
@@ -150,3 +159,54 @@ class GenerationLoop:
             finally:
                 be.finish(slots)
         return results  # type: ignore[return-value]
+
+    def _run_ahead(self, be, sampler, active, toks, toks_dev, slot_of, out, results, lens, budgets, reasons, stop,
+                   on_step) -> None:
+        """The decode loop with one step of lookahead: step n+1 is launched on the tokens that step
+        n sampled while they are still on the device; the host reads them meanwhile and learns one
+        step late that a request has stopped.  Such a request has then been fed one token too
+        many, which nobody sees: its result ends at the stop token and its slot is freed with the
+        batch.  The tokens, their order and the reasons are those of the plain loop; the sampler
+        must not need the host's history of a request."""
+        pending, keep = None, None       # the copy of `toks_dev` under way, and which of its rows are `active`
+        while True:
+            # Requests that go on unless the token they are about to receive is a stop token.
+            # Their step is launched now, on the device's copy of those tokens; the host reads
+            # the tokens while that step runs.
+            rows = [i for i, r in enumerate(active) if len(out[r]) + 1 < budgets[r]]
+            ahead = [active[i] for i in rows]
+            nxt_pending = nxt_dev = None
+            if ahead:
+                feed = toks_dev if len(rows) == len(active) else toks_dev[torch.tensor(rows, device=toks_dev.device)]
+                logits = be.decode([slot_of[r] for r in ahead], feed)
+                nxt_dev = sampler.sample(logits, ahead)
+                nxt_pending = be.read_tokens_async(nxt_dev)
+                self.stats.n_decode_steps += 1
+            if pending is not None:
+                got = pending.wait()
+                toks = got if keep is None else [got[i] for i in keep]
+            live, emitted = [], {}
+            for r, tok in zip(active, toks):
+                tok = int(tok)
+                if tok in stop:
+                    results[r] = GenerationResult(out[r], "stop", lens[r], stop_token=tok)
+                    continue
+                out[r].append(tok)
+                emitted[r] = tok
+                sampler.accept(r, [tok])
+                self.stats.n_gen += 1
+                if len(out[r]) >= budgets[r]:
+                    results[r] = GenerationResult(out[r], reasons[r], lens[r])
+                    continue
+                live.append(r)
+            if on_step is not None and emitted:
+                on_step(emitted)
+            if not live:
+                if nxt_pending is not None:
+                    nxt_pending.wait()      # nothing of the step that ran ahead is used
+                return
+            keep = None
+            if live != ahead:                # some request stopped: its row of the step that ran ahead is dropped
+                keep = [ahead.index(r) for r in live]
+                nxt_dev = nxt_dev[torch.tensor(keep, device=nxt_dev.device)]
+            active, toks_dev, pending = live, nxt_dev, nxt_pending

@@ -134,6 +134,13 @@ class Sampler:
         self.draws = [0] * n_requests
         self.breakers = tuple(breakers)
 
+    @property
+    def needs_history(self) -> bool:
+        """Whether sampling a request's next token needs its earlier tokens on the host (the
+        repetition and DRY penalties do); if not, a step may be launched before the host has read
+        the previous step's tokens."""
+        return self.p.repeat_penalty != 1.0 or self.p.dry_multiplier != 0.0
+
     def accept(self, request: int, tokens: Sequence[int]) -> None:
         """Records tokens that entered the context, prompt or generated (src/sampler.zig:84-89)."""
         h = self.history[request]
