@@ -187,3 +187,33 @@ def test_errors_leave_the_engine_usable(model_folders):
     assert ok.shape == (1, 256) and torch.isfinite(ok).all()
     eng.finish(slots)
     eng.cache.check_consistency()
+
+
+@pytest.mark.parametrize("temp", [0.0, 0.9])
+def test_running_one_step_ahead_changes_no_token(model_folders, temp):
+    """The loop that launches a step before the host has read the previous tokens gives the
+    tokens, stop reasons and order of the plain loop: unequal prompts, budgets that end requests
+    at different steps, and stop tokens that end some requests in mid-batch (learned one step
+    late by the loop that runs ahead)."""
+    import zinfer_b200 as z
+    folder = model_folders["tiny_b"]
+    model = z.load(folder, dtype="float32")
+    vocab = model.config.vocab_size
+    prompts = [helpers.random_tokens(700 + i, n, vocab) for i, n in enumerate([3, 17, 40, 9, 26, 1])]
+    plain = z.Engine(model, max_batch=4, max_seq_len=256, page_size=16, lookahead=False)
+    ahead = z.Engine(model, max_batch=4, max_seq_len=256, page_size=16)
+    free = plain.generate(prompts, max_new_tokens=24, temp=temp, seed=5, stop_ids=[])
+    # stop tokens: what some requests emit at their 5th and 11th place
+    stops = sorted({free[1].tokens[4], free[4].tokens[10], free[2].tokens[0]})
+    for stop_ids, budget in (([], 24), (stops, 24), (stops, 7)):
+        seen = []
+        a = plain.generate(prompts, max_new_tokens=budget, temp=temp, seed=5, stop_ids=stop_ids)
+        b = ahead.generate(prompts, max_new_tokens=budget, temp=temp, seed=5, stop_ids=stop_ids,
+                           on_step=lambda d: seen.append(dict(d)))
+        assert [(r.tokens, r.finish_reason, r.stop_token) for r in a] == [(r.tokens, r.finish_reason, r.stop_token) for r in b]
+        assert ahead.stats.n_gen == plain.stats.n_gen
+        for i, r in enumerate(b):       # the callback saw every emitted token, in order
+            assert [d[i] for d in seen if i in d] == r.tokens
+    assert any(r.finish_reason == "stop" for r in b) and any(r.finish_reason != "stop" for r in b)
+    plain.cache.check_consistency()
+    ahead.cache.check_consistency()

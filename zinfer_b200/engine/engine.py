@@ -88,7 +88,7 @@ class Engine:
     def __init__(self, model: Model, max_batch: int = 64, max_seq_len: Optional[int] = None,
                  max_tokens: Optional[int] = None, page_size: int = 64, max_step_tokens: int = 8192,
                  attn_split_keys: int = 0, use_graphs: bool = True, fused_decode: bool = False,
-                 fused_decode_max_context: int = 4096):
+                 fused_decode_max_context: int = 4096, lookahead: bool = True):
         """max_batch: slots (sequences alive at once).  max_seq_len: longest sequence, default
         the model's max_position_embeddings.  max_tokens: tokens the cache holds in total, each
         sequence rounded up to whole pages; default max_batch * max_seq_len.  max_step_tokens:
@@ -99,7 +99,9 @@ class Engine:
         no sequence is longer than fused_decode_max_context (that kernel does not split a
         sequence's keys over blocks).  Off by default: measured on a B200 it is slower than the
         graph of separate kernels (its per-operation barrier and input staging cost what a kernel
-        boundary costs, and its contraction loop issues more instructions per byte)."""
+        boundary costs, and its contraction loop issues more instructions per byte).  lookahead:
+        `generate` launches a step before the host has read the previous step's tokens whenever
+        the sampler allows it."""
         kernels.require_cuda()
         if model.device is None:
             raise ValueError("the model has no weights loaded")
@@ -118,6 +120,7 @@ class Engine:
         self.status = kernels.status_word(self.device)      # one status word per device, shared by all kernels
         self.vocab_size = cfg.vocab_size
         self.use_graphs = bool(use_graphs)
+        self.supports_device_tokens = bool(lookahead)    # GenerationLoop asks this before running ahead
         self.fused_decode = bool(fused_decode) and self.use_graphs
         self.fused_decode_max_context = int(fused_decode_max_context)
         self._fused: dict[int, _DecodeGraph] = {}
@@ -222,7 +225,6 @@ class Engine:
         return self.model.forward(ctx, self.calls, want_rows)
 
     # ------------------------------------------------------------------ single-token steps
-    supports_device_tokens = True   # `decode` takes the tokens as an int32 tensor on the device too
 
     def decode(self, slots: Sequence[int], tokens, check: bool = False) -> torch.Tensor:
         """One token for each sequence, logits [len(slots), vocab] for all of them.  The same
