@@ -112,10 +112,13 @@ class StepContext:
         if not self.is_decode or self.max_kv_len <= 0:
             return 1, 0
         keys = self._split_keys
-        if keys <= 0:                     # about four blocks per SM, chunks of at least 128 keys
+        if keys <= 0:
+            # about four blocks per SM, chunks of 128 to 4096 keys: with unequal sequences a longer
+            # chunk leaves the SMs that drew a short sequence idle (64 sequences of 1K to 32K tokens:
+            # 3.90 ms a step with chunks of 16K keys, 3.27 ms with 4K)
             blocks = max(1, self.n_seqs * n_kv_heads)
             want = max(1, -(-592 // blocks))
-            keys = max(128, -(-self.max_kv_len // want))
+            keys = min(4096, max(128, -(-self.max_kv_len // want)))
             keys = -(-keys // 64) * 64
         n = -(-self.max_kv_len // keys)
         return (n, keys) if n > 1 else (1, 0)
