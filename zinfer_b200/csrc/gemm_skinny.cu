@@ -129,13 +129,73 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   // much arithmetic (many tokens) or a norm prologue can hide them, else at the top of the loop;
   // measured, not derived.
   constexpr bool PIPE = NT >= 4 || NORM;
-  if (PIPE) load_w(s_begin);
+  // The register-resident norm prologue below (up to 8 rows) holds a thread's share of the rows;
+  // the first weights are then requested after it, not before, so that the two do not add up.
+  const bool norm_in_registers = NORM && NT == 1 && K <= WARPS * 32 * 8;
+  if (PIPE && !norm_in_registers) load_w(s_begin);
 
   // NORM: the block normalises the M rows once into shared memory as bfloat16 (row stride padded
   // by 16 bytes so that the 8 rows a fragment load touches fall into different banks).
   const int xs_ld = K + 8;
   if constexpr (NORM) {
     float* part = row_scale + NT * 8;  // [NT * 8][WARPS] partial sums of squares
+    constexpr int TH = WARPS * 32;
+    if (norm_in_registers) {
+      // Up to 8 rows of up to 2 float4 per thread: every value is loaded once, all loads are under
+      // way together, and the rows stay in registers between the sum and the scaling.  A row's sum
+      // is added in the same order as below (per thread over k, over the lanes, over the warps).
+      float4 v[8][2], w[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int k = threadIdx.x * 4 + j * TH * 4;
+        w[j] = k < K ? *reinterpret_cast<const float4*>(a.norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          v[m][j] = (m < M && k < K) ? *reinterpret_cast<const float4*>(a.Xf + (size_t)m * a.ldx + k)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (threadIdx.x * 4 + j * TH * 4 < K) {
+            ss = fmaf(v[m][j].x, v[m][j].x, ss);
+            ss = fmaf(v[m][j].y, v[m][j].y, ss);
+            ss = fmaf(v[m][j].z, v[m][j].z, ss);
+            ss = fmaf(v[m][j].w, v[m][j].w, ss);
+          }
+        }
+        const float t = warp_sum(ss);
+        if (lane == 0 && m < M) part[m * WARPS + warp] = t;
+      }
+      __syncthreads();
+      if (threadIdx.x < M) {
+        float t = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < WARPS; ++ww) t += part[threadIdx.x * WARPS + ww];
+        row_scale[threadIdx.x] = 1.0f / sqrtf(t / (float)K + a.eps);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        if (m < M) {
+          const float sc = row_scale[m];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int k = threadIdx.x * 4 + j * TH * 4;
+            if (k < K) {
+              uint2 pk;
+              pk.x = pack2((v[m][j].x * sc) * w[j].x, (v[m][j].y * sc) * w[j].y);
+              pk.y = pack2((v[m][j].z * sc) * w[j].z, (v[m][j].w * sc) * w[j].w);
+              *reinterpret_cast<uint2*>(xs + (size_t)m * xs_ld + k) = pk;
+            }
+          }
+        }
+      }
+      __syncthreads();
+      load_w(s_begin);
+    } else {
     for (int m0 = 0; m0 < M; m0 += 4) {
       float ss[4] = {0.f, 0.f, 0.f, 0.f};
       for (int k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4) {
@@ -188,6 +248,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
       }
     }
     __syncthreads();
+    }
   }
 
   bool xok[NT];
