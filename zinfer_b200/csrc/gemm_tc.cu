@@ -379,17 +379,28 @@ __global__ void __launch_bounds__(THREADS)
         const unsigned rank = cluster_rank();
         if (n < p.N) {
           const float b = p.bias ? p.bias[n] : 0.f;
-          for (int t = (int)rank; t < p.M; t += p.splits) {
-            float pv[8];
+          // four tokens at a time: their remote partials (up to 8 blocks in a cluster) and old
+          // values are all requested before the first sum, so a thread waits for them once, not
+          // once per token
+          for (int t0 = (int)rank; t0 < p.M; t0 += 4 * p.splits) {
+            float pv[4][8], old[4];
 #pragma unroll
-            for (int z = 0; z < 8; ++z)   // up to 8 blocks in a cluster; the loads are independent
-              pv[z] = z < p.splits ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
-            TC* dst = C + (size_t)t * p.ldc + n;
-            const float old = p.accumulate ? to_f32(*dst) : 0.f;
-            float acc = b;
+            for (int i = 0; i < 4; ++i) {
+              const int t = t0 + i * p.splits;
 #pragma unroll
-            for (int z = 0; z < 8; ++z) acc += pv[z];
-            *dst = from_f32<TC>(acc + old);
+              for (int z = 0; z < 8; ++z)
+                pv[i][z] = (t < p.M && z < p.splits) ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
+              old[i] = (t < p.M && p.accumulate) ? to_f32(C[(size_t)t * p.ldc + n]) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int t = t0 + i * p.splits;
+              if (t >= p.M) break;
+              float acc = b;
+#pragma unroll
+              for (int z = 0; z < 8; ++z) acc += pv[i][z];
+              C[(size_t)t * p.ldc + n] = from_f32<TC>(acc + old[i]);
+            }
           }
         }
       }
