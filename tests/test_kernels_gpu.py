@@ -430,7 +430,9 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
                          H, Hkv, hd, n_rot, inter, eps, status)
         bq, _ = k.attn_tile_shape(H, Hkv)
         if kind == "prompt_tc":
-            bq = k.attention_plan(dtype, H, Hkv, hd, page, False)[1]
+            bq = k._fn("attention_prefill", "zk_attn_prefill_tile_tokens")(H, Hkv)
+        if kind == "prompt_tc5":
+            bq = k._fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(H, Hkv)
         tiles = torch.from_numpy(attn_tiles_host(step_lens, bq)).cuda()
         return k.attention(q, setup.k, setup.v, tiles[0].contiguous(), tiles[1].contiguous(), cu_q, seq_start,
                            seq_slot, setup.table_dev, H, Hkv, hd, scale, 0, num_splits, split_keys, single_token, kind)
@@ -442,9 +444,14 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
         q, kk, v = reference(i, l)
         ref.append(attn_ref(q, kk, v, 0, 0, scale).reshape(l, H * hd))
     close(out, torch.cat(ref), dtype, "prefill attention")
-    if k.attention_plan(dtype, H, Hkv, hd, page, False)[0] == "prompt_tc":
+    if dtype == torch.bfloat16 and k._takes("attention_prefill", "zk_attn_prefill_takes", H, Hkv, hd, page):
         again = run(lens, [0] * len(lens), torch.cat([s[:-1] for s in seqs]), kind="prompt_tc")
         close(again, torch.cat(ref), dtype, "prefill attention on the tensor cores")
+        assert not torch.isnan(again.float()).any()
+    if k.attention_plan(dtype, H, Hkv, hd, page, False)[0] == "prompt_tc5":
+        again = run(lens, [0] * len(lens), torch.cat([s[:-1] for s in seqs]), kind="prompt_tc5")
+        assert status.item() == 0 and k.status_word("cuda").item() == 0
+        close(again, torch.cat(ref), dtype, "prefill attention with tcgen05")
         assert not torch.isnan(again.float()).any()
     last = torch.stack([s[-1] for s in seqs])
     ref = []

@@ -31,6 +31,11 @@ _STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's posit
                 11: "a tensor-core contraction gave up waiting for a free pipeline stage",
                 12: "a tensor-core contraction gave up waiting for its operand tiles",
                 13: "a tensor-core contraction gave up waiting for its accumulator",
+                14: "the tcgen05 prompt attention gave up waiting for a free K/V stage",
+                15: "the tcgen05 prompt attention gave up waiting for its query or K/V tiles",
+                16: "the tcgen05 prompt attention gave up waiting for the probabilities",
+                17: "the tcgen05 prompt attention gave up waiting for the scores",
+                18: "the tcgen05 prompt attention gave up waiting for P V",
                 21: "the one-kernel single-token step gave up waiting at a grid barrier",
                 22: "the one-kernel single-token step was given an operation it does not take"}
 

@@ -59,6 +59,11 @@ _SIGNATURES = {
         "zk_attn_prefill_takes": "iiii",
         "zk_attn_prefill_tile_tokens": "ii",
     },
+    "attention_prefill_tc5": {
+        "zk_attn_prefill_tc5": "pppppppppp" + "iii" + "l" + "iiii" + "f" + "pp",
+        "zk_attn_prefill_tc5_takes": "iiiii",
+        "zk_attn_prefill_tc5_tile_tokens": "ii",
+    },
     "attention_decode_tc": {
         "zk_attn_decode_tc": "pppppppppiiiiiiifiip",
         "zk_attn_decode_tc_takes": "iiii",
@@ -527,6 +532,8 @@ def _may_take(lib: str, n_heads: int, n_kv: int, head_dim: int, page_size: int) 
         return head_dim in (64, 128) and group <= 16 and page_size % 64 == 0
     if lib == "attention_prefill":
         return head_dim in (64, 128) and page_size % 64 == 0
+    if lib == "attention_prefill_tc5":
+        return head_dim == 64 and page_size % 64 == 0
     raise KeyError(lib)
 
 
@@ -535,10 +542,13 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
 
 
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                   single_token: bool) -> tuple[str, int]:
+                   single_token: bool, window: int = 0) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
-    ("single_token_tc" | "single_token" | "prompt_tc" | "general", tokens per tile)."""
+    ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile)."""
     if dtype == torch.bfloat16 and n_heads % n_kv == 0:
+        if (not single_token and window <= 0 and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
+                and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
+            return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
         if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token_tc", 1
         if single_token and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
@@ -573,6 +583,17 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if num_splits > 1:
         part_o = torch.empty((num_splits, n * n_heads, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
+    if kind == "prompt_tc5":
+        if (q.dtype != torch.bfloat16 or window > 0 or not k_cache.is_contiguous() or not v_cache.is_contiguous()
+                or not q.is_contiguous()
+                or not _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
+            raise KernelError("attention: the tcgen05 prompt kernel does not take these sizes")
+        _check(_fn("attention_prefill_tc5", "zk_attn_prefill_tc5")(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
+            _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, k_cache.shape[0],
+            n_heads, n_kv, head_dim, page_size, scale, _ptr(status_word(q.device)), _stream()),
+            "attention (prompt, tcgen05)")
+        return out
     if kind == "prompt_tc":
         if q.dtype != torch.bfloat16 or not _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim,
                                                    page_size):

@@ -88,7 +88,7 @@ class GqaAttention(Mixer):
             q = kernels.qk_prepare(normed, kv.k, kv.v, None, None, None, n_rot=0, interleaved=False,
                                    write_kv=call.writes_kv, **common)
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
-                                                   ctx.is_decode)
+                                                   ctx.is_decode, self.window)
         tile_seq, tile_q0 = ctx.attn_tiles(tile_tokens)
         num_splits, split_keys = ctx.kv_splits(self.n_kv)
         att = kernels.attention(q, kv.k, kv.v, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot,
