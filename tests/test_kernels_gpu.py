@@ -581,3 +581,57 @@ def test_size_predicates_known_to_python_agree_with_the_libraries(k):
             for hd in (16, 32, 48, 64, 80, 96, 128, 256):
                 for page in (16, 32, 64, 96, 128):
                     assert bool(k._fn(lib, fn)(H, Hkv, hd, page)) == k._may_take(lib, H, Hkv, hd, page), (lib, H, Hkv, hd, page)
+
+
+@pytest.mark.parametrize("H,Hkv,page", [(32, 8, 64), (6, 2, 128), (16, 1, 64), (5, 5, 64)])
+def test_tcgen05_prompt_attention_far_key_and_continued_prompt(k, H, Hkv, page):
+    """The tcgen05 prompt kernel on a prompt cut in two steps (the second continues at position
+    500 and ends in the middle of a key tile), with one far key that must win for every query
+    that sees it, NaN in every cache row that no token has written, and a second short sequence
+    in the same batch."""
+    from zinfer_b200.engine.context import attn_tiles_host
+    dtype, hd = torch.bfloat16, 64
+    assert k.attention_plan(dtype, H, Hkv, hd, page, False)[0] == "prompt_tc5"
+    T, cut, far = 731, 500, 37
+    scale = 1 / math.sqrt(hd)
+    kk = rnd((T, Hkv, hd), 1, dtype, 0.3)
+    v = rnd((T, Hkv, hd), 2, dtype)
+    q = rnd((T, H, hd), 3, dtype, 0.3)
+    kk[far] = 0
+    kk[far, :, 0] = 12.0
+    q[:, :, 0] = 12.0
+    k2, v2, q2 = rnd((9, Hkv, hd), 4, dtype, 0.3), rnd((9, Hkv, hd), 5, dtype), rnd((9, H, hd), 6, dtype, 0.3)
+    setup = PagedSetup([T, 9], [2, 0], 4, page, Hkv, hd, dtype, seed=3)
+    for slot, (kx, vx) in ((2, (kk, v)), (0, (k2, v2))):
+        n = kx.shape[0]
+        pages = torch.from_numpy(setup.table[slot, :-(-n // page)].astype(np.int64)).cuda()
+        pad = (-n) % page
+        fill = torch.full((pad, Hkv, hd), float("nan"), dtype=dtype)
+        setup.k[pages] = torch.cat([kx, fill]).reshape(-1, page, Hkv, hd).permute(0, 2, 1, 3).cuda()
+        setup.v[pages] = torch.cat([vx, fill]).reshape(-1, page, Hkv, hd).permute(0, 2, 1, 3).cuda()
+    bq = k._fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(H, Hkv)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    g = H // Hkv
+    ref1 = attn_ref(q.double(), kk.double(), v.double(), 0, 0, scale)
+    ref2 = attn_ref(q2.double(), k2.double(), v2.double(), 0, 0, scale)
+    # step 1: the first 500 tokens of the long sequence and the whole short one
+    lens, starts = [cut, 9], [0, 0]
+    tiles = torch.from_numpy(attn_tiles_host(lens, bq)).cuda()
+    rows = torch.cat([q[:cut].reshape(cut, H * hd), q2.reshape(9, H * hd)]).cuda()
+    out = k.attention(rows, setup.k, setup.v, tiles[0].contiguous(), tiles[1].contiguous(), i32([0, cut, cut + 9]),
+                      i32(starts), i32([2, 0]), setup.table_dev, H, Hkv, hd, scale, kind="prompt_tc5")
+    assert k.status_word("cuda").item() == 0 and not torch.isnan(out.float()).any()
+    close(out[:cut], ref1[:cut].reshape(cut, H * hd), dtype, "first step of the long prompt")
+    close(out[cut:], ref2.reshape(9, H * hd), dtype, "the short prompt beside it")
+    # step 2: the long sequence goes on at position 500
+    n2 = T - cut
+    tiles = torch.from_numpy(attn_tiles_host([n2], bq)).cuda()
+    out2 = k.attention(q[cut:].reshape(n2, H * hd).cuda(), setup.k, setup.v, tiles[0].contiguous(), tiles[1].contiguous(),
+                       i32([0, n2]), i32([cut]), i32([2]), setup.table_dev, H, Hkv, hd, scale, kind="prompt_tc5")
+    assert k.status_word("cuda").item() == 0 and not torch.isnan(out2.float()).any()
+    close(out2, ref1[cut:].reshape(n2, H * hd), dtype, "continued prompt")
+    winner = v[far].float()[[h // g for h in range(H)]]
+    for t in (far, far + 1, cut - 1):
+        assert torch.allclose(out[t].float().cpu().reshape(H, hd), winner, atol=0.05), f"query {t} did not pick the far key"
+    assert torch.allclose(out2[-1].float().cpu().reshape(H, hd), winner, atol=0.05)
+    assert not torch.allclose(out[far - 1].float().cpu().reshape(H, hd), winner, atol=0.05), "a later key was seen"
