@@ -22,16 +22,16 @@
 //
 // Every wait on an mbarrier is bounded: after about two seconds the block records a code in
 // *status, stops issuing work, frees its tensor memory and returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace tc5;   // mbarrier, TMA, tensor-memory and tcgen05.mma wrappers; descriptors
 
 constexpr int BM = 128;          // tile rows = accumulator lanes
 constexpr int BK = 64;           // k block: 64 bfloat16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;     // producer warp, MMA warp, four epilogue warps
-constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds of SM clock
 
 struct Params {
   void* C;
@@ -41,76 +41,6 @@ struct Params {
   int ldc, accumulate, splits;
   int swiglu;          // normal mode: W rows are groups of 16 gate rows + their 16 up rows; C [M, N/2] = silu(g)*u
 };
-
-// ------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false = gave up after WAIT_CYCLES.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > WAIT_CYCLES) return false;
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                          unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-// 16 consecutive float32 columns of this thread's accumulator lane
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, float v[16]) {
-  unsigned r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      "tcgen05.wait::ld.sync.aligned;\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 // Thread-block cluster: barrier over all threads of all blocks, rank, and loads from another
 // block's shared memory.
@@ -128,22 +58,6 @@ __device__ __forceinline__ float ld_remote_f32(unsigned local_smem_addr, unsigne
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride byte offset), version 1, swizzle mode 2.
-__device__ __forceinline__ unsigned long long smem_desc(const void* tile) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_u32(tile) & 0x3FFFF) >> 4);   // start address
-  d |= (unsigned long long)1 << 16;                             // leading byte offset (unused with swizzle)
-  d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset
-  d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
-  d |= (unsigned long long)2 << 61;                             // 128-byte swizzle
-  return d;
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, shape M x N.
-__device__ __forceinline__ unsigned instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
 template <int BN, int STAGES>
