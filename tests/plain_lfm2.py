@@ -161,13 +161,15 @@ def short_conv(xn, w_in, conv_w, w_out, conv_b=None, b_in=None, b_out=None, dtyp
 
 
 def gqa_attention(xn, wq, wk, wv, wo, q_norm_w, k_norm_w, n_heads, n_kv, hd, eps, inv_freq,
-                  window=0, dtype=np.float32, cache_round=None):
+                  window=0, dtype=np.float32, cache_round=None, encode=None):
     """Grouped-query attention over a whole sequence (src/model.zig:1715-1991):
     q,k,v projections; per-head RMSNorm of q and k with the layer eps
     (src/model.zig:1741-1744, 1760-1763); RoPE; causal scores (q.k)*1/sqrt(hd)
     (src/attention.zig:486); softmax; PV; query head h reads KV head h // (H/Hkv)
     (src/model.zig:1330, 1360); keys [max(0, p+1-window), p] (src/model.zig:1362-1363).
-    `cache_round` (a function) rounds q, k and v the way a reduced-precision cache would."""
+    `cache_round` (a function) rounds q, k and v the way a reduced-precision cache would.
+    `encode` (a function (q, k, positions) -> (q, k)) stands for another position encoding, run
+    where the rotation runs; tests of parts that are not the reference's use it."""
     T, _ = xn.shape
     xn = xn.astype(dtype)
     q = (xn @ wq.astype(dtype).T).reshape(T, n_heads, hd)
@@ -180,6 +182,8 @@ def gqa_attention(xn, wq, wk, wv, wo, q_norm_w, k_norm_w, n_heads, n_kv, hd, eps
     if inv_freq is not None:
         q = apply_rope(q, pos, inv_freq, dtype)
         k = apply_rope(k, pos, inv_freq, dtype)
+    if encode is not None:
+        q, k = encode(q, k, pos)
     if cache_round is not None:
         q, k, v = cache_round(q).astype(dtype), cache_round(k).astype(dtype), cache_round(v).astype(dtype)
     g = n_heads // n_kv

@@ -330,3 +330,149 @@ def test_prenorm_block_part(k, dtype, mixer_kind):
         bench.done(slot, [1])
         got[t] = stream[0].cpu()
     close(got, ref, dtype, "stream after the block")
+
+
+# ------------------------------------------------------------------------------- parts of the test's own
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Hkv,hd,page", [(3, 1, 48, 16), (4, 2, 64, 64)])
+def test_attention_takes_a_position_encoding_of_another_kind(k, dtype, H, Hkv, hd, page):
+    """A position encoding defined here that is no rotation table: learned vectors per absolute
+    position, added to the normalised q and k.  The attention part runs it between its norm and
+    its cache write, in prompt steps and in single-token steps."""
+    from zinfer_b200.parts import POSITION_ENCODINGS, GqaAttention, PositionEncoding, WeightSpec
+
+    class LearnedPositions(PositionEncoding):
+        def __init__(self, head_dim, n_pos, q_name, k_name):
+            self.head_dim, self.n_pos, self.q_name, self.k_name = head_dim, n_pos, q_name, k_name
+
+        def weight_specs(self):
+            return [WeightSpec(self.q_name, (self.n_pos, self.head_dim)), WeightSpec(self.k_name, (self.n_pos, self.head_dim))]
+
+        def load(self, weights, dtype, device):
+            self.tq, self.tk = weights[self.q_name], weights[self.k_name]
+
+        def apply(self, ctx, q, k):
+            pos = ctx.tok_pos.long()
+            q.unflatten(1, (-1, self.head_dim)).add_(self.tq[pos][:, None, :])
+            k.unflatten(1, (-1, self.head_dim)).add_(self.tk[pos][:, None, :])
+
+    POSITION_ENCODINGS.register("toy_learned", LearnedPositions, replace=True)
+    try:
+        D, eps = 80, 1e-5
+        tensors = {"q": rnd((H * hd, D), 70, dtype, 0.3), "k": rnd((Hkv * hd, D), 71, dtype, 0.3),
+                   "v": rnd((Hkv * hd, D), 72, dtype, 0.3), "o": rnd((D, H * hd), 73, dtype, 0.3),
+                   "qn": 1.0 + rnd((hd,), 74, dtype, 0.3), "kn": 1.0 + rnd((hd,), 75, dtype, 0.3),
+                   "pq": rnd((96, hd), 76, dtype, 0.7), "pk": rnd((96, hd), 77, dtype, 0.7)}
+        enc = POSITION_ENCODINGS.get("toy_learned")(hd, 96, "pq", "pk")
+        assert enc.rotary() is None
+        mixer = load(GqaAttention(D, H, Hkv, hd, "q", "k", "v", "o", "qn", "kn", eps, enc), tensors, dtype)
+        xs = [rnd((n, D), 80 + n, dtype) for n in (70, 33)]
+        outs = run_mixer(k, mixer, dtype, xs, [52, 33 - 4], page=page)
+        f = lambda name: tensors[name].numpy().astype(np.float64)
+        encode = lambda q, kk, pos: (q + f("pq")[pos][:, None, :], kk + f("pk")[pos][:, None, :])
+        for b, x in enumerate(xs):
+            ref = P.gqa_attention(x.numpy(), f("q"), f("k"), f("v"), f("o"), f("qn"), f("kn"), H, Hkv, hd, eps, None, 0,
+                                  np.float64, encode=encode)
+            close(outs[b], ref, dtype, f"sequence {b}")
+        bare = P.gqa_attention(xs[1].numpy(), f("q"), f("k"), f("v"), f("o"), f("qn"), f("kn"), H, Hkv, hd, eps, None, 0,
+                               np.float64)
+        assert np.abs(bare - ref).max() > 1e-2 * np.abs(ref).max(), "the encoding must change the result"
+    finally:
+        POSITION_ENCODINGS.unregister("toy_learned")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [1, 7, 40])
+def test_feed_forward_with_routing_of_the_tests_own(k, dtype, rows):
+    """A feed-forward defined here that routes: router logits in float32, the best two of four
+    experts per row, their softmax as weights; the experts are the library's SwiGLU parts, nested
+    so that their weights are found through `parts()`.  Registered, built by name, run alone and
+    inside a block."""
+    from zinfer_b200.parts import FEED_FORWARDS, FeedForward, PreNormBlock, RMSNorm, ShortConv, SwiGLU, WeightSpec
+
+    class TopTwo(FeedForward):
+        def __init__(self, hidden, ffn_dim, n_experts, prefix):
+            self.hidden, self.n_experts, self.router_name = hidden, n_experts, prefix + "router"
+            self.experts = [SwiGLU(hidden, ffn_dim, f"{prefix}{e}.w1", f"{prefix}{e}.w3", f"{prefix}{e}.w2")
+                            for e in range(n_experts)]
+
+        def parts(self):
+            return list(self.experts)
+
+        def weight_specs(self):
+            return [WeightSpec(self.router_name, (self.n_experts, self.hidden))]
+
+        def load(self, weights, dtype, device):
+            self.router = weights[self.router_name]
+
+        def forward(self, ctx, xn, out, accumulate):
+            logits = xn.float() @ self.router.float().t()
+            top, idx = logits.topk(2, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            total = torch.zeros_like(out)
+            for e, expert in enumerate(self.experts):
+                hit = (idx == e)
+                rows_e = hit.any(-1).nonzero().flatten()
+                if rows_e.numel() == 0:
+                    continue
+                y = torch.empty((rows_e.numel(), self.hidden), dtype=torch.float32, device=out.device)
+                expert.forward(ctx, xn[rows_e].contiguous(), y, False)
+                total[rows_e] += y * (gate * hit)[rows_e].sum(-1, keepdim=True)
+            if accumulate:
+                out += total
+            else:
+                out.copy_(total)
+
+    FEED_FORWARDS.register("toy_top_two", TopTwo, replace=True)
+    try:
+        D, F, E = 96, 112, 4
+        tensors = {"f.router": rnd((E, D), 90, dtype, 1.0), "n1": 1.0 + rnd((D,), 91, dtype, 0.2),
+                   "n2": 1.0 + rnd((D,), 92, dtype, 0.2), "in": rnd((3 * D, D), 93, dtype, 0.2),
+                   "conv": rnd((D, 3), 94, dtype, 0.5), "out": rnd((D, D), 95, dtype, 0.2)}
+        for e in range(E):
+            tensors.update({f"f.{e}.w1": rnd((F, D), 100 + e, dtype, 0.2), f"f.{e}.w3": rnd((F, D), 110 + e, dtype, 0.2),
+                            f"f.{e}.w2": rnd((D, F), 120 + e, dtype, 0.2)})
+        ffn = load(FEED_FORWARDS.get("toy_top_two")(D, F, E, "f."), tensors, dtype)
+        f = lambda name: tensors[name].numpy().astype(np.float64)
+
+        def plain(xn):
+            logits = xn @ f("f.router").T
+            out = np.zeros_like(xn)
+            used = set()
+            for t in range(xn.shape[0]):
+                best = np.argsort(-logits[t])[:2]
+                assert logits[t][best[1]] - np.sort(logits[t])[-3] > 1e-3, "routing too close to call"
+                g = np.exp(logits[t][best] - logits[t][best[0]])
+                g /= g.sum()
+                for w, e in zip(g, best):
+                    out[t] += w * P.swiglu(xn[t:t + 1], f(f"f.{e}.w1"), f(f"f.{e}.w3"), f(f"f.{e}.w2"), np.float64)[0]
+                    used.add(int(e))
+            return out, used
+
+        bench = Bench(k, norm_free_mixer(), dtype)
+        ctx = bench.step(bench.cache.alloc_slots(1), [rows])
+        xn = rnd((rows, D), 130, dtype)
+        ref, used = plain(xn.numpy().astype(np.float64))
+        assert rows < 7 or len(used) == E
+        out = torch.full((rows, D), 2.0, device="cuda")
+        ffn.forward(ctx, xn.to(dtype).cuda(), out, False)
+        close(out, ref, dtype, "alone")
+
+        # inside a block, after a mixer: the routing then sees the block's own normalised rows, so the
+        # reference takes them from the norm part and only the feed-forward is compared
+        mixer = ShortConv(D, 3, "in", "conv", "out")
+        block = load(PreNormBlock(RMSNorm(D, 1e-5, "n1"), mixer, RMSNorm(D, 1e-5, "n2"), ffn), tensors, dtype)
+        bench = Bench(k, mixer, dtype)
+        slot = bench.cache.alloc_slots(1)
+        ctx = bench.step(slot, [rows])
+        x = rnd((rows, D), 131, torch.float32).cuda()
+        after_mixer = x.clone()
+        block.mixer.forward(ctx, bench.call, block.mixer_norm.forward(ctx, after_mixer, lazy=True), after_mixer, True)
+        xn2 = block.ffn_norm.forward(ctx, after_mixer).float().cpu().numpy().astype(np.float64)
+        ref2, _ = plain(xn2)
+        bench.call.state.zero_()                  # the same step again through the block, from an empty state
+        block.forward(ctx, bench.call, x)
+        close(x - after_mixer, ref2, dtype, "in a block")
+    finally:
+        FEED_FORWARDS.unregister("toy_top_two")
