@@ -137,6 +137,35 @@ def test_gemm_tc_prompt_shapes(k, M, N, K):
     assert k.status_word("cuda").item() == 0
 
 
+@pytest.mark.parametrize("form", [0, 256, 512])
+@pytest.mark.parametrize("M,N,K,swiglu", [(256, 256, 64, False), (2048, 2048, 2048, False), (700, 1024, 520, False),
+                                          (130, 768, 8200, False), (1100, 512, 192, True), (2048, 4096, 1024, True)])
+def test_gemm_tc_forms_agree(k, form, M, N, K, swiglu):
+    """The three forms of a prompt-step product (one tile per block, persistent blocks, persistent
+    pairs of blocks with tcgen05.mma.cta_group::2) each against the plain product: row tails that
+    leave the second block of a pair without rows, K tails, every way of storing."""
+    a = rnd((M, K), 15, torch.bfloat16).cuda()
+    w = rnd((N, K), 16, torch.bfloat16, 0.1).cuda()
+    ref = a.double() @ w.double().T
+    k.gemm_tc_force_form(form)
+    try:
+        if swiglu:
+            g = ref.reshape(M, N // 32, 2, 16)
+            act = (g[:, :, 0] / (1 + torch.exp(-g[:, :, 0])) * g[:, :, 1]).reshape(M, N // 2)
+            close(k.gemm_tc(a, w, swiglu=True), act, torch.bfloat16, "swiglu")
+        else:
+            close(k.gemm_tc(a, w, out_dtype=torch.float32), ref, torch.float32, "f32 out")
+            close(k.gemm_tc(a, w), ref, torch.bfloat16, "bf16 out")
+            res = rnd((M, N), 18, torch.float32).cuda()
+            res0 = res.clone()
+            k.gemm_tc(a, w, out=res, accumulate=True)
+            close(res, ref + res0.double(), torch.float32, "accumulate")
+        torch.cuda.synchronize()
+        assert k.status_word("cuda").item() == 0
+    finally:
+        k.gemm_tc_force_form(-1)
+
+
 @pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 6144, 2048, 1), (8, 2048, 8192, 8), (16, 331 * 8, 2048, 3),
                                           (17, 2048, 2048, 4), (33, 100, 520, 2), (64, 16384, 2048, 2), (5, 65536, 256, 1)])
 def test_gemm_tc_single_token_shapes(k, M, N, K, splits):

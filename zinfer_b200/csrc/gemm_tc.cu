@@ -335,35 +335,63 @@ __global__ void __launch_bounds__(THREADS)
 // warps store tile i while the MMA warp works on tile i + 1, so the tensor cores do not wait for
 // stores.  The epilogue stages 64 columns at a time in a shared-memory buffer of its own (the
 // ring is never free here) and writes whole lines.
-template <int BN, int STAGES>
+// NV outputs of this thread's row into its 128-byte row of a staging tile with 128-byte swizzle: the
+// 16-byte chunk c of row r lies at chunk c ^ (r & 7).  `chunk0` is the first chunk they fill.
+template <typename TC, int NV>
+__device__ __forceinline__ void stage_row(unsigned char* row, int r, int chunk0, const float* v) {
+  constexpr int PER = 16 / (int)sizeof(TC);   // outputs in a chunk
+#pragma unroll
+  for (int i = 0; i < NV / PER; ++i) {
+    uint4 q;
+    if constexpr (sizeof(TC) == 4) {
+      q = make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]), __float_as_uint(v[4 * i + 2]),
+                     __float_as_uint(v[4 * i + 3]));
+    } else {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+      q = make_uint4(*reinterpret_cast<unsigned*>(&h0), *reinterpret_cast<unsigned*>(&h1), *reinterpret_cast<unsigned*>(&h2),
+                     *reinterpret_cast<unsigned*>(&h3));
+    }
+    *reinterpret_cast<uint4*>(row + (((chunk0 + i) ^ (r & 7)) << 4)) = q;
+  }
+}
+
+template <int BN, int STAGES, bool PAIR>
 struct SmemP {
-  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;            // weight rows this block loads per stage
+  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int EW = 64, LD = EW + 1;                 // staged columns, odd row stride
-  static constexpr int EPI_BYTES = BM * LD * 4;
+  static constexpr int PIECE_BYTES = 32 * 128;               // 32 rows x 128 bytes of output: one TMA store
+  static constexpr int EPI_BYTES = 4 * 2 * PIECE_BYTES;      // two staging tiles for each epilogue warp
   static constexpr size_t BYTES = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN, int STAGES, typename TC>
-__global__ void __launch_bounds__(THREADS)
+template <int BN, int STAGES, bool PAIR, typename TC>
+__global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
     gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                              const Params p) {
+                              const __grid_constant__ CUtensorMap map_c, const Params p) {
   extern __shared__ unsigned char smem_raw[];
-  using S = SmemP<BN, STAGES>;
+  using S = SmemP<BN, STAGES, PAIR>;
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* stage = reinterpret_cast<float*>(tiles + (size_t)STAGES * S::STAGE_BYTES);
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(tiles + (size_t)STAGES * S::STAGE_BYTES + S::EPI_BYTES);
+  unsigned char* stage_base = tiles + (size_t)STAGES * S::STAGE_BYTES;   // 1024-byte aligned, as the swizzle needs
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(stage_base + S::EPI_BYTES);
   unsigned long long* empty = full + STAGES;
   unsigned long long* acc_full = empty + STAGES;     // [2]
   unsigned long long* acc_empty = acc_full + 2;      // [2]
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_ok = aborted + 1;   // [4]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr unsigned TMEM_COLS = 2 * BN;
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "tensor memory holds two accumulators");
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  // A unit is a block, or a pair of blocks (ranks 0 and 1 of a cluster) that shares 256 x BN tiles:
+  // each block of a pair loads its 128 token rows and its half of the BN weight rows, the block of
+  // rank 0 issues the pair's MMAs, and each block stores the 128 x BN accumulator of its own rows.
+  const unsigned rank = PAIR ? cluster_rank() : 0u;
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TM = PAIR ? 2 * BM : BM;     // token rows of a unit's tile
+  const int tiles_m = (p.M + TM - 1) / TM, tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int nkb = (p.K + BK - 1) / BK;
 
@@ -374,22 +402,26 @@ __global__ void __launch_bounds__(THREADS)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);   // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], PAIR ? 8 : 4);   // one arrival per epilogue warp (of both blocks of a pair)
     }
     *aborted = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    else tmem_alloc(tmem_slot, TMEM_COLS);
+  }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the other block's barriers are initialised before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
     int it = 0;
-    for (int t = blockIdx.x; t < n_tiles && !*aborted; t += gridDim.x) {
+    for (int t = unit; t < n_tiles && !*aborted; t += n_units) {
       const int a_tile = t % tiles_m, b_tile = t / tiles_m;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % STAGES;
@@ -400,16 +432,24 @@ __global__ void __launch_bounds__(THREADS)
         }
         if (*aborted) break;
         unsigned char* a_dst = tiles + (size_t)s * S::STAGE_BYTES;
-        mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, kb * BK, a_tile * BM, &full[s]);
-        tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN, &full[s]);
+        if constexpr (PAIR) {
+          // both blocks' bytes are counted on the barrier of rank 0, where the MMAs are issued
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * S::STAGE_BYTES);
+          const unsigned bar = cluster_addr(&full[s], 0);
+          tma_load_2d_pair(a_dst, &map_a, kb * BK, a_tile * TM + (int)rank * BM, bar);
+          tma_load_2d_pair(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN + (int)rank * S::B_ROWS, bar);
+        } else {
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, kb * BK, a_tile * BM, &full[s]);
+          tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN, &full[s]);
+        }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1 && lane == 0 && rank == 0) {
     // ---------------------------------------------------------------- MMA issuer
-    const unsigned idesc = instr_desc(BM, BN);
+    const unsigned idesc = instr_desc(TM, BN);
     int it = 0, local = 0;
-    for (int t = blockIdx.x; t < n_tiles && !*aborted; t += gridDim.x, ++local) {
+    for (int t = unit; t < n_tiles && !*aborted; t += n_units, ++local) {
       const int buf = local & 1;
       if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1)) {   // the epilogue has read this accumulator
         atomicExch(p.status, 13);
@@ -431,128 +471,105 @@ __global__ void __launch_bounds__(THREADS)
         const unsigned char* a_src = tiles + (size_t)s * S::STAGE_BYTES;
         const unsigned long long da = smem_desc(a_src), db = smem_desc(a_src + S::A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_bf16(d_tmem, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&empty[s]);
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          if constexpr (PAIR)
+            umma_bf16_pair(d_tmem, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
+                           (kb > 0 || k > 0) ? 1u : 0u);
+          else
+            umma_bf16(d_tmem, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        if constexpr (PAIR) umma_commit_pair(&empty[s]);   // frees the stage in both blocks
+        else umma_commit(&empty[s]);
       }
       if (!ok) break;
-      umma_commit(&acc_full[buf]);
+      if constexpr (PAIR) umma_commit_pair(&acc_full[buf]);
+      else umma_commit(&acc_full[buf]);
     }
   } else if (warp >= 2) {
     // ---------------------------------------------------------------- epilogue
+    // Each warp stores the 32 accumulator rows that it may read, on its own: 32 columns at a time
+    // from tensor memory into registers (one thread per row), the outputs as pieces of 128 bytes
+    // per row into one of its two staging tiles (128-byte swizzle, as the map of C expects), and
+    // lane 0 hands the tile to the TMA: a store, or an add to what C holds (the residual sum).
+    // The TMA leaves out rows past M.
     const int quarter = warp & 3;            // the 32 accumulator lanes this warp may read
-    const int row = quarter * 32 + lane;     // row of the tile
-    constexpr int EW = S::EW, LD = S::LD;
-    int local = 0;
-    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++local) {
+    unsigned char* my_stage = stage_base + quarter * (2 * S::PIECE_BYTES);
+    constexpr int OUTC = 128 / (int)sizeof(TC);                   // output columns of a piece
+    const int groups_per_piece = OUTC / (p.swiglu ? 16 : 32);     // 32 accumulator columns give 32 outputs, or 16
+    int local = 0, sb = 0;
+    for (int t = unit; t < n_tiles; t += n_units, ++local) {
       const int a_tile = t % tiles_m, b_tile = t / tiles_m;
+      const int m0 = a_tile * TM + (int)rank * BM + quarter * 32;   // first token row of this warp
       const int buf = local & 1;
       const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
-      // The four warps go on or leave together (they meet at named barriers below): each posts
-      // what it saw, all read all four after a barrier.
-      if (lane == 0) epi_ok[quarter] = ok && !*aborted;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!(epi_ok[0] && epi_ok[1] && epi_ok[2] && epi_ok[3])) {
+      if (!__all_sync(0xffffffffu, ok) || *aborted) {
         if (!ok && lane == 0) atomicExch(p.status, 13);
         *aborted = 1;
         break;
       }
       tc_fence_after();
       const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN);
+      const int x_tile = b_tile * (p.swiglu ? BN / 2 : BN);
 #pragma unroll 1
-      for (int e0 = 0; e0 < BN; e0 += EW) {
-        // float32 output that is added to: this lane's old values of the 64 columns (rows of its
-        // warp, columns lane and lane + 32) are requested now, all at once; they arrive while the
-        // accumulator is read.  (One block of 192 threads per SM: registers are plentiful.)
-        float old[32][2];
-        if constexpr (sizeof(TC) == 4) {
-          if (p.accumulate && !p.swiglu) {
-            const int n_base = b_tile * BN + e0;
-#pragma unroll
-            for (int r = 0; r < 32; ++r) {
-              const int m = a_tile * BM + quarter * 32 + r;
-              const float* crow = reinterpret_cast<const float*>(p.C) + (size_t)m * p.ldc + n_base;
-#pragma unroll
-              for (int i = 0; i < 2; ++i)
-                old[r][i] = (m < p.M && n_base + lane + 32 * i < p.N) ? crow[lane + 32 * i] : 0.f;
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // the previous 64 columns have been stored
-#pragma unroll
-        for (int c0 = 0; c0 < EW; c0 += 16) {
-          float v[16];
-          tmem_ld16(lane_addr + e0 + c0, v);   // warp-collective
-#pragma unroll
-          for (int j = 0; j < 16; ++j) stage[row * LD + c0 + j] = v[j];
-        }
-        if (e0 + EW == BN) {   // every column of the accumulator is in registers or shared memory
+      for (int g = 0; g < BN / 32; ++g) {
+        float v[32];
+        tmem_ld32(lane_addr + (unsigned)(g * 32), v);   // warp-collective
+        if (g == BN / 32 - 1) {   // the whole accumulator has been read: the MMA warp may overwrite it
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
+            else mbar_arrive(&acc_empty[buf]);
+          }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (p.swiglu) {
-          // columns: 16 gates, their 16 ups, ...: EW/2 outputs per row
-          const int h_base = b_tile * (BN / 2) + e0 / 2, F = p.N / 2;
-          for (int r = quarter * 32; r < quarter * 32 + 32; ++r) {
-            const int m = a_tile * BM + r;
-            if (m >= p.M) break;
-            TC* hrow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc + h_base;
-            const float* srow = stage + r * LD;
-            const int gc = (lane / 16) * 32 + (lane % 16);      // this output's gate column; the up is 16 further
-            if (h_base + lane < F) {
-              const float gate = srow[gc], up = srow[gc + 16];
-              hrow[lane] = from_f32<TC>(gate / (1.0f + expf(-gate)) * up);
-            }
-          }
+        const int part = g % groups_per_piece;
+        if (part == 0) {   // a new piece: the store before last has read this staging tile
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+        }
+        unsigned char* row = my_stage + sb * S::PIECE_BYTES + lane * 128;
+        if (p.swiglu) {    // columns: 16 gates, then their 16 ups
+          float o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = v[j] / (1.0f + expf(-v[j])) * v[j + 16];
+          stage_row<TC, 16>(row, lane, part * (16 * (int)sizeof(TC) / 16), o);
         } else {
-          const int n_base = b_tile * BN + e0;
+          if (p.bias) {
+            const float* b = p.bias + b_tile * BN + g * 32;
 #pragma unroll
-          for (int rr = 0; rr < 32; ++rr) {
-            const int r = quarter * 32 + rr;
-            const int m = a_tile * BM + r;
-            if (m >= p.M) break;
-            TC* crow = reinterpret_cast<TC*>(p.C) + (size_t)m * p.ldc + n_base;
-            const float* srow = stage + r * LD;
-            if constexpr (sizeof(TC) == 4) {
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const int col = lane + 32 * i;
-                const float o = p.accumulate ? old[rr][i] : 0.f;
-                if (n_base + col < p.N) crow[col] = o + srow[col] + (p.bias ? p.bias[n_base + col] : 0.f);
-              }
-            } else {
-              const int col = 2 * lane;
-              if (n_base + col + 1 < p.N && (p.ldc & 1) == 0) {
-                float o0 = srow[col] + (p.bias ? p.bias[n_base + col] : 0.f);
-                float o1 = srow[col + 1] + (p.bias ? p.bias[n_base + col + 1] : 0.f);
-                __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(crow + col);
-                if (p.accumulate) {
-                  const __nv_bfloat162 old = *dst;
-                  o0 += __low2float(old);
-                  o1 += __high2float(old);
-                }
-                *dst = __floats2bfloat162_rn(o0, o1);
-              } else {
-                for (int e = 0; e < 2; ++e)
-                  if (n_base + col + e < p.N) {
-                    float o = srow[col + e] + (p.bias ? p.bias[n_base + col + e] : 0.f);
-                    if (p.accumulate) o += to_f32(crow[col + e]);
-                    crow[col + e] = from_f32<TC>(o);
-                  }
-              }
-            }
+            for (int j = 0; j < 32; ++j) v[j] += b[j];
           }
+          stage_row<TC, 32>(row, lane, part * (32 * (int)sizeof(TC) / 16), v);
+        }
+        if (part == groups_per_piece - 1) {
+          fence_async_smem();   // the staged rows are visible to the TMA
+          __syncwarp();
+          if (lane == 0) {
+            if (m0 < p.M) {
+              const int x = x_tile + (g / groups_per_piece) * OUTC;
+              if (p.accumulate) tma_reduce_add_2d(&map_c, my_stage + sb * S::PIECE_BYTES, x, m0);
+              else tma_store_2d(&map_c, my_stage + sb * S::PIECE_BYTES, x, m0);
+            }
+            // a group for every piece, an empty one for rows past M: "all but the newest group" above
+            // then always means the store that read the other staging tile
+            bulk_commit();
+          }
+          sb ^= 1;
         }
       }
     }
+    if (lane == 0) bulk_wait_all();   // the stores are complete before the block ends
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if constexpr (PAIR) {
+    cluster_sync_all();   // neither block leaves, or frees tensor memory, while the pair's MMAs may still use it
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  } else {
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 // ------------------------------------------------------------------------------ host side
@@ -585,6 +602,20 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int b
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Map of the output C [rows, cols] (row stride ld elements) for stores of 32 rows x 128 bytes.
+bool make_out_map(CUtensorMap* map, void* base, int rows, int cols, int ld, bool f32) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const int elt = f32 ? 4 : 2;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * elt};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / elt), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, int STAGES, bool SWAP, typename TC>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, STAGES, SWAP, TC>;
@@ -606,18 +637,37 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
   return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
 }
 
-template <int BN, int STAGES, typename TC>
-int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int n_tiles, cudaStream_t stream) {
-  auto kern = gemm_tc_persistent_kernel<BN, STAGES, TC>;
-  const size_t smem = SmemP<BN, STAGES>::BYTES;
-  static_assert(SmemP<BN, STAGES>::BYTES <= 227 * 1024, "shared memory of one block");
+// `n_tiles` tiles of the unit's size (128 x BN, or 256 x BN for pairs); one block per SM at most.
+template <int BN, int STAGES, bool PAIR, typename TC>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const Params& p, int n_tiles,
+                      cudaStream_t stream) {
+  auto kern = gemm_tc_persistent_kernel<BN, STAGES, PAIR, TC>;
+  const size_t smem = SmemP<BN, STAGES, PAIR>::BYTES;
+  static_assert(SmemP<BN, STAGES, PAIR>::BYTES <= 227 * 1024, "shared memory of one block");
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return ZK_EINVAL;
-  kern<<<n_tiles < sms ? n_tiles : sms, THREADS, smem, stream>>>(ma, mb, p);
-  return ZK_LAUNCH_STATUS();
+  if constexpr (!PAIR) {
+    kern<<<n_tiles < sms ? n_tiles : sms, THREADS, smem, stream>>>(ma, mb, mc, p);
+    return ZK_LAUNCH_STATUS();
+  } else {
+    const int units = n_tiles < sms / 2 ? n_tiles : sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * units);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;   // blocks 2u and 2u + 1 are the pair u
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p);
+  }
 }
 
 // Which form a prompt-step product takes: 0 = one 128 x 128 tile per block, 256 = persistent blocks
@@ -625,8 +675,13 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const Params
 // reads a quarter less per multiply-add, but needs several tiles per SM to do so.  Measured on the
 // LFM2-1.2B shapes (whole prompt step): 2,048 tokens 7.65 ms with form 0, 7.59 with form 256
 // everywhere; 8,192 tokens 34.4 against 32.5 ms.
+// 512 = the persistent form with pairs of blocks on 256 x 256 tiles (tcgen05.mma.cta_group::2): each
+// block loads half of the weight tile, so a multiply-add needs half the bytes from L2 that a
+// 128 x 128 tile needs.
+int forced_form = -1;   // set by zk_gemm_tc_force_form for measurements and tests; -1 = choose
 int normal_form(int M, int N) {
   if (N % 256) return 0;
+  if (forced_form >= 0) return forced_form;
   const int tiles = ceil_div_i(M, BM) * (N / 256);
   return tiles >= 2 * 148 ? 256 : 0;
 }
@@ -650,15 +705,24 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   Params p{};
   p.C = C; p.bias = bias; p.status = status;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1; p.swiglu = swiglu;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc;
   const bool f32 = out_dtype == ZK_F32;
   if (M > 64) {
-    if (normal_form(M, N) == 256) {
+    // the persistent forms store through the TMA: rows of C 16-byte aligned, and an add only in float32
+    const bool tma_out = (ldc * (f32 ? 4 : 2)) % 16 == 0 && (f32 || !accumulate);
+    const int form = tma_out ? normal_form(M, N) : 0;
+    if (form == 512 || form == 256) {
       constexpr int BW = 256;
-      if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, N, K, ldw, BW)) return ZK_EINVAL;
-      const int n_tiles = ceil_div_i(M, BM) * ceil_div_i(N, BW);
-      return f32 ? launch_persistent<BW, 4, float>(ma, mb, p, n_tiles, stream)
-                 : launch_persistent<BW, 4, bf16>(ma, mb, p, n_tiles, stream);
+      const bool pair = form == 512;
+      if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, N, K, ldw, pair ? BW / 2 : BW) ||
+          !make_out_map(&mc, C, M, swiglu ? N / 2 : N, ldc, f32))
+        return ZK_EINVAL;
+      const int n_tiles = ceil_div_i(M, pair ? 2 * BM : BM) * ceil_div_i(N, BW);
+      if (pair)
+        return f32 ? launch_persistent<BW, 6, true, float>(ma, mb, mc, p, n_tiles, stream)
+                   : launch_persistent<BW, 6, true, bf16>(ma, mb, mc, p, n_tiles, stream);
+      return f32 ? launch_persistent<BW, 4, false, float>(ma, mb, mc, p, n_tiles, stream)
+                 : launch_persistent<BW, 4, false, bf16>(ma, mb, mc, p, n_tiles, stream);
     }
     constexpr int BN = 128;
     if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, N, K, ldw, BN)) return ZK_EINVAL;
@@ -681,6 +745,14 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   if (bn == 32) { ZK_TC_SWAP(32) }
   ZK_TC_SWAP(64)
 #undef ZK_TC_SWAP
+}
+
+// Forces the form of products with more than 64 rows and N a multiple of 256: 0 one 128 x 128 tile
+// per block, 256 persistent blocks, 512 persistent pairs of blocks; -1 gives the choice back.
+int zk_gemm_tc_force_form(int form) {
+  if (form != -1 && form != 0 && form != 256 && form != 512) return ZK_EINVAL;
+  forced_form = form;
+  return 0;
 }
 
 }  // extern "C"

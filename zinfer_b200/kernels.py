@@ -40,6 +40,7 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "zk_gemm_tc": "ppppiiiiiiiiiipp",
+        "zk_gemm_tc_force_form": "i",
     },
     "shortconv": {
         "zk_conv_forward": "ppppppppiiiliip",
@@ -298,6 +299,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
                                         1 if swiglu else 0, _ptr(status_word(a.device)), _stream()),
            "gemm_tc")
     return out
+
+
+def gemm_tc_force_form(form: int) -> None:
+    """For measurements and tests: the form that products of more than 64 rows with N a multiple of
+    256 take.  0 = one 128 x 128 tile per block, 256 = persistent blocks with 128 x 256 tiles, 512 =
+    persistent pairs of blocks with 256 x 256 tiles (tcgen05.mma.cta_group::2); -1 = the library chooses."""
+    _check(_fn("gemm_tc", "zk_gemm_tc_force_form")(int(form)), "gemm_tc_force_form")
 
 
 def gemm_skinny_max_m() -> int:
