@@ -329,12 +329,14 @@ __global__ void __launch_bounds__(THREADS)
 }
 
 // ------------------------------------------------------------------------------ persistent form
-// Prompt steps with many tiles: one block per SM walks the 128 x BN tiles (token tiles fastest, so
-// that the blocks running together share weight tiles in L2).  The stage ring runs on across
-// tiles, the accumulator is double-buffered in tensor memory (2 x BN columns), and the epilogue
-// warps store tile i while the MMA warp works on tile i + 1, so the tensor cores do not wait for
-// stores.  The epilogue stages 64 columns at a time in a shared-memory buffer of its own (the
-// ring is never free here) and writes whole lines.
+// Products of more than 64 rows with N a multiple of 256: one block per SM walks the tiles (token
+// tiles fastest, so that the blocks running together share weight tiles in L2).  The stage ring
+// runs on across tiles, the accumulator is double-buffered in tensor memory (2 x BN columns), and
+// the epilogue warps store tile i while the MMA warp works on tile i + 1.  With PAIR two blocks of
+// a cluster share 256 x BN tiles through tcgen05.mma.cta_group::2.  The epilogue goes from tensor
+// memory through registers and a swizzled staging tile to a TMA store (or a TMA reduce-add for the
+// float32 residual sum): a per-row loop of ordinary loads and stores in its place held these
+// kernels at 0.8-0.9 PFLOP/s; without any stores they ran at 1.4.
 // NV outputs of this thread's row into its 128-byte row of a staging tile with 128-byte swizzle: the
 // 16-byte chunk c of row r lies at chunk c ^ (r & 7).  `chunk0` is the first chunk they fill.
 template <typename TC, int NV>
@@ -670,20 +672,20 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
   }
 }
 
-// Which form a prompt-step product takes: 0 = one 128 x 128 tile per block, 256 = persistent blocks
-// with 128 x 256 tiles.  The persistent form overlaps a tile's stores with the next tile's MMAs and
-// reads a quarter less per multiply-add, but needs several tiles per SM to do so.  Measured on the
-// LFM2-1.2B shapes (whole prompt step): 2,048 tokens 7.65 ms with form 0, 7.59 with form 256
-// everywhere; 8,192 tokens 34.4 against 32.5 ms.
-// 512 = the persistent form with pairs of blocks on 256 x 256 tiles (tcgen05.mma.cta_group::2): each
-// block loads half of the weight tile, so a multiply-add needs half the bytes from L2 that a
-// 128 x 128 tile needs.
+// Which form a product of more than 64 rows takes: 0 = one 128 x 128 tile per block; 256 = persistent
+// blocks with 128 x 256 tiles; 512 = persistent pairs of blocks with 256 x 256 tiles
+// (tcgen05.mma.cta_group::2: each block loads half of the weight tile, so a multiply-add needs half
+// the bytes from L2 and from shared memory that a 128 x 128 tile needs).  The persistent forms
+// overlap a tile's stores with the next tile's MMAs and store through the TMA; they take N a
+// multiple of 256.  Measured on the LFM2-1.2B shapes with 2,048 rows (TFLOP/s, forms 0 / 256 / 512):
+// w1|w3 786 / 1291 / 1321, w2 848 / 1181 / 1272, in_proj 787 / 1177 / 1275, qkv 605 / 819 / 865,
+// out_proj 536 / 825 / 820; with 256 rows the pairs still lead, with 128 rows a pair's second block
+// has no rows and single blocks are chosen.
 int forced_form = -1;   // set by zk_gemm_tc_force_form for measurements and tests; -1 = choose
 int normal_form(int M, int N) {
   if (N % 256) return 0;
   if (forced_form >= 0) return forced_form;
-  const int tiles = ceil_div_i(M, BM) * (N / 256);
-  return tiles >= 2 * 148 ? 256 : 0;
+  return M > 128 ? 512 : 256;
 }
 
 }  // namespace
