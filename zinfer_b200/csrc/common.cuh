@@ -52,3 +52,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
+
+// ------------------------------------------------------------------------------ dependent launches
+// A kernel launched with zk_launch_dependent may start while the kernel before it in the stream is
+// still running: its blocks take the places of blocks that have ended, do whatever needs nothing
+// of that kernel (index arithmetic, the first loads of weights), and then call zk_wait_prior(),
+// which returns when every kernel before it is complete and its memory is visible.  NOTHING that
+// an earlier kernel writes may be read, and nothing may be written, before zk_wait_prior().
+// zk_let_next_start() lets the kernel after this one be launched in the same way; with no call
+// it starts when this kernel's blocks have ended.  Both are no-ops in a kernel launched plainly.
+__device__ __forceinline__ void zk_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void zk_let_next_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline int zk_launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}

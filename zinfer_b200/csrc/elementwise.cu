@@ -44,6 +44,8 @@ __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const int* __re
                                     const float* __restrict__ w, TO* __restrict__ y, int dim, float eps) {
   __shared__ float scratch[32];
   const int r = blockIdx.x;
+  zk_let_next_start();
+  zk_wait_prior();   // x is the kernel before's result
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
   const int n4 = dim >> 2;
   float4 v[4];
@@ -160,10 +162,8 @@ int zk_rmsnorm(const float* x, const int* rows, const float* w, void* y, int n_o
   if (dim % 4 == 0 && dim <= 16 * threads && aligned && (out_dtype == ZK_F32 || out_dtype == ZK_BF16)) {
     while (threads > 32 && threads * 4 >= 2 * dim) threads >>= 1;   // no idle warps for short rows
     if (out_dtype == ZK_F32)
-      rmsnorm_vec4_kernel<float><<<n_out, threads, 0, stream>>>(x, rows, w, (float*)y, dim, eps);
-    else
-      rmsnorm_vec4_kernel<bf16><<<n_out, threads, 0, stream>>>(x, rows, w, (bf16*)y, dim, eps);
-    return ZK_LAUNCH_STATUS();
+      return zk_launch_dependent(rmsnorm_vec4_kernel<float>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, (float*)y, dim, eps);
+    return zk_launch_dependent(rmsnorm_vec4_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, (bf16*)y, dim, eps);
   }
   if (out_dtype == ZK_F32)
     rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(x, rows, w, (float*)y, dim, eps);

@@ -132,7 +132,9 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   // The register-resident norm prologue below (up to 8 rows) holds a thread's share of the rows;
   // the first weights are then requested after it, not before, so that the two do not add up.
   const bool norm_in_registers = NORM && NT == 1 && K <= WARPS * 32 * 8;
-  if (PIPE && !norm_in_registers) load_w(s_begin);
+  if ((PIPE && !norm_in_registers) || !PIPE) load_w(s_begin);   // weights need nothing of the kernel before
+  zk_let_next_start();
+  zk_wait_prior();   // the rows (X, Xf, the convolution's state) and C are the kernels' before
 
   // NORM: the block normalises the M rows once into shared memory as bfloat16 (row stride padded
   // by 16 bytes so that the 8 rows a fragment load touches fall into different banks).
@@ -265,7 +267,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
       for (int i = 0; i < 4; ++i) acc[r][t][i] = 0.f;
 
   for (int s = s_begin; s < s_end; s += UNROLL) {
-    if (!PIPE) load_w(s);
+    if (!PIPE && s != s_begin) load_w(s);
     uint4 xv[UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -373,7 +375,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   if (task >= n_tasks) break;
   __syncthreads();   // the epilogue has read `red`
   set_task();
-  if (PIPE) load_w(s_begin);
+  load_w(s_begin);
   }
 }
 
@@ -400,8 +402,7 @@ int launch(const Args& a, cudaStream_t stream) {
   }
   int grid = ceil_div_i(a.N, EPI == EPI_PLAIN ? 16 * RG : 16);
   if (NORM && grid > norm_grid_cap()) grid = norm_grid_cap();   // the norm prologue once for several tasks
-  kern<<<grid, WARPS * 32, smem, stream>>>(a);
-  return ZK_LAUNCH_STATUS();
+  return zk_launch_dependent(kern, dim3(grid), dim3(WARPS * 32), smem, stream, a);
 }
 
 // Shapes are chosen so that a block streams enough weights to pay for its start-up and so that an
