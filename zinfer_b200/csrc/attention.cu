@@ -36,6 +36,7 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   int hd, int n_rot, int interleaved, float eps, int page_size, int write_kv,
                                   int* status) {
   __shared__ float sm_all[ATT_WARPS][ATT_MAX_HD];
+  zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = H + 2 * Hkv;
   const long long item = (long long)blockIdx.x * ATT_WARPS + warp;
@@ -347,6 +348,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   T* __restrict__ out, int n_rows, int hd, int num_splits) {
+  zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -472,11 +474,11 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
   const long long items = (long long)n_tokens * (H + 2 * Hkv);
   const int blocks = (int)((items + ATT_WARPS - 1) / ATT_WARPS);
   if (dtype == ZK_F32)
-    qk_prepare_kernel<float><<<blocks, ATT_WARPS * 32, 0, stream>>>(
+    return zk_launch_dependent(qk_prepare_kernel<float>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream,
         (const float*)qkv, (float*)q_out, (float*)dense_out, (float*)k_cache, (float*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos,
         seq_slot, page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status);
   else if (dtype == ZK_BF16)
-    qk_prepare_kernel<bf16><<<blocks, ATT_WARPS * 32, 0, stream>>>(
+    return zk_launch_dependent(qk_prepare_kernel<bf16>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream,
         (const bf16*)qkv, (bf16*)q_out, (bf16*)dense_out, (bf16*)k_cache, (bf16*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot,
         page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status);
   else
@@ -512,9 +514,9 @@ int zk_attn_merge(const float* part_o, const float* part_ml, void* out, int n_ro
   const int warps = 4;
   const int blocks = (n_rows + warps - 1) / warps;
   if (dtype == ZK_F32)
-    attn_merge_kernel<float><<<blocks, warps * 32, 0, stream>>>(part_o, part_ml, (float*)out, n_rows, hd, num_splits);
+    return zk_launch_dependent(attn_merge_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, (float*)out, n_rows, hd, num_splits);
   else if (dtype == ZK_BF16)
-    attn_merge_kernel<bf16><<<blocks, warps * 32, 0, stream>>>(part_o, part_ml, (bf16*)out, n_rows, hd, num_splits);
+    return zk_launch_dependent(attn_merge_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, (bf16*)out, n_rows, hd, num_splits);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();

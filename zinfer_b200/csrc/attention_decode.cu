@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
   __shared__ float sm_m[DEC_WARPS][G], sm_l[DEC_WARPS][G];
   __shared__ float sm_o[DEC_WARPS][G][HD];
 
+  zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int H = Hkv * G;
@@ -211,7 +212,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
            const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int Hkv,
            int page_size, int window, float scale, int num_splits, int split_keys, cudaStream_t stream) {
   dim3 grid(n_seqs, Hkv, num_splits);
-  attn_decode_kernel<VPL, G><<<grid, DEC_WARPS * 32, 0, stream>>>(
+  return zk_launch_dependent(attn_decode_kernel<VPL, G>, grid, dim3(DEC_WARPS * 32), 0, stream,
       (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, part_ml, seq_start, seq_slot,
       page_table, pt_stride, n_seqs, Hkv, page_size, window, scale, num_splits, split_keys);
   return ZK_LAUNCH_STATUS();

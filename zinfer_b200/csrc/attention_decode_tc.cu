@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   unsigned char* Ksm[2] = {smem, smem + 2 * TILE_BYTES};
   unsigned char* Vsm[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES};
 
+  zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int G = H / Hkv;
@@ -265,7 +266,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_seqs, Hkv, num_splits);
-  kern<<<grid, DT_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
+  return zk_launch_dependent(kern, grid, dim3(DT_WARPS * 32), smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H, Hkv,
                                               page_size, window, scale, num_splits, split_keys);
   return ZK_LAUNCH_STATUS();

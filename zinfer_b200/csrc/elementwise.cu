@@ -8,6 +8,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x,
                              int dim, int vocab, float scale, int* status) {
+  zk_let_next_start();
+  zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int t = blockIdx.x;
   const int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;

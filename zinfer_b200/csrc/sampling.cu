@@ -253,6 +253,8 @@ __global__ void penalties_kernel(float* __restrict__ logits, int V, const int* _
 // Lowest index among the largest logits of each row (src/sampler.zig:532-610).
 __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
   __shared__ Shared sh;
+  zk_let_next_start();
+  zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const float* row = logits + (size_t)blockIdx.x * V;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
