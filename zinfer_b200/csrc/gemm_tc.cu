@@ -107,7 +107,23 @@ __global__ void __launch_bounds__(THREADS)
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
-    for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+    // The operand that holds weights needs nothing of the kernel before this one: its tiles of the
+    // first stages are requested, the next kernel is let in, and only then does the producer wait
+    // for the kernel before and request the rows.
+    const CUtensorMap* map_w = SWAP ? &map_a : &map_b;
+    const CUtensorMap* map_x = SWAP ? &map_b : &map_a;
+    const int w_row = SWAP ? a_tile * BM : b_tile * BN, x_row = SWAP ? b_tile * BN : a_tile * BM;
+    constexpr int W_OFF = SWAP ? 0 : S::A_BYTES, X_OFF = SWAP ? S::A_BYTES : 0;
+    const int pre = min(STAGES, kb1 - kb0);
+    for (int it = 0; it < pre; ++it) {
+      mbar_expect_tx(&full[it], S::STAGE_BYTES);
+      tma_load_2d(tiles + (size_t)it * S::STAGE_BYTES + W_OFF, map_w, (kb0 + it) * BK, w_row, &full[it]);
+    }
+    zk_let_next_start();
+    zk_wait_prior();
+    for (int it = 0; it < pre; ++it)
+      tma_load_2d(tiles + (size_t)it * S::STAGE_BYTES + X_OFF, map_x, (kb0 + it) * BK, x_row, &full[it]);
+    for (int kb = kb0 + pre, it = pre; kb < kb1; ++kb, ++it) {
       const int s = it % STAGES;
       if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
         atomicExch(p.status, 11);
@@ -146,6 +162,7 @@ __global__ void __launch_bounds__(THREADS)
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;            // the 32 accumulator lanes this warp may read
     const int row = quarter * 32 + lane;     // row of the tile
+    zk_wait_prior();                         // C, which this warp reads and writes, is the kernels' before
     bool ok = mbar_wait(acc_done, 0);
     if (!ok) {
       if (lane == 0) atomicExch(p.status, 13);
@@ -422,10 +439,34 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
-    int it = 0;
+    // The weights need nothing of the kernel before this one: the weight tiles of the first tile's
+    // first stages are requested, the next kernel is let in, and only then does the producer wait
+    // for the kernel before and request the rows.
+    const int pre = unit < n_tiles ? min(STAGES, nkb) : 0;
+    const unsigned bar0 = PAIR ? cluster_addr(&full[0], 0) : 0u;   // stage s: bar0 + 8 s
+    for (int s = 0; s < pre; ++s) {
+      unsigned char* b_dst = tiles + (size_t)s * S::STAGE_BYTES + S::A_BYTES;
+      const int b_tile = unit / tiles_m;
+      if constexpr (PAIR) {
+        if (rank == 0) mbar_expect_tx(&full[s], 2 * S::STAGE_BYTES);
+        tma_load_2d_pair(b_dst, &map_b, s * BK, b_tile * BN + (int)rank * S::B_ROWS, bar0 + 8u * s);
+      } else {
+        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+        tma_load_2d(b_dst, &map_b, s * BK, b_tile * BN, &full[s]);
+      }
+    }
+    zk_let_next_start();
+    zk_wait_prior();
+    for (int s = 0; s < pre; ++s) {
+      unsigned char* a_dst = tiles + (size_t)s * S::STAGE_BYTES;
+      const int a_tile = unit % tiles_m;
+      if constexpr (PAIR) tma_load_2d_pair(a_dst, &map_a, s * BK, a_tile * TM + (int)rank * BM, bar0 + 8u * s);
+      else tma_load_2d(a_dst, &map_a, s * BK, a_tile * BM, &full[s]);
+    }
+    int it = pre;
     for (int t = unit; t < n_tiles && !*aborted; t += n_units) {
       const int a_tile = t % tiles_m, b_tile = t / tiles_m;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int kb = (t == unit ? pre : 0); kb < nkb; ++kb, ++it) {
         const int s = it % STAGES;
         if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
           atomicExch(p.status, 11);
@@ -496,6 +537,7 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
     // lane 0 hands the tile to the TMA: a store, or an add to what C holds (the residual sum).
     // The TMA leaves out rows past M.
     const int quarter = warp & 3;            // the 32 accumulator lanes this warp may read
+    zk_wait_prior();                         // C, which this warp stores to or adds to, is the kernels' before
     unsigned char* my_stage = stage_base + quarter * (2 * S::PIECE_BYTES);
     constexpr int OUTC = 128 / (int)sizeof(TC);                   // output columns of a piece
     const int groups_per_piece = OUTC / (p.swiglu ? 16 : 32);     // 32 accumulator columns give 32 outputs, or 16
@@ -629,13 +671,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;   // the blocks that split K form one cluster
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = p.splits;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits for the one before by itself
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;   // the blocks that split K form one cluster
+  attr[1].val.clusterDim.x = 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = p.splits;
   cfg.attrs = attr;
-  cfg.numAttrs = p.splits > 1 ? 1 : 0;
+  cfg.numAttrs = p.splits > 1 ? 2 : 1;
   return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
 }
 
@@ -652,8 +696,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return ZK_EINVAL;
   if constexpr (!PAIR) {
-    kern<<<n_tiles < sms ? n_tiles : sms, THREADS, smem, stream>>>(ma, mb, mc, p);
-    return ZK_LAUNCH_STATUS();
+    return zk_launch_dependent(kern, dim3(n_tiles < sms ? n_tiles : sms), dim3(THREADS), smem, stream, ma, mb, mc, p);
   } else {
     const int units = n_tiles < sms / 2 ? n_tiles : sms / 2;
     cudaLaunchConfig_t cfg = {};
@@ -661,13 +704,15 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;   // blocks 2u and 2u + 1 are the pair u
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits for the one before by itself
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p);
   }
 }

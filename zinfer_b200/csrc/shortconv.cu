@@ -141,6 +141,8 @@ __global__ void conv_decode_kernel(const T* __restrict__ bcx, float* __restrict_
                                    T* __restrict__ y, int n_seqs, int D, int K, long long state_slot_stride, int il) {
   const int ch = blockIdx.y * blockDim.x + threadIdx.x;
   const int b = blockIdx.x;
+  zk_let_next_start();
+  zk_wait_prior();   // bcx is the kernel before's result
   if (ch >= D || b >= n_seqs) return;
   float* st = state + (size_t)seq_slot[b] * state_slot_stride;
   const T* row = bcx + (size_t)b * 3 * D;
@@ -211,14 +213,12 @@ int zk_conv_decode(const void* bcx, float* state, const float* w, const float* b
   const int threads = 128;
   dim3 grid(n_seqs, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
-    conv_decode_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, w, bias, seq_slot, (float*)y,
-                                                            n_seqs, D, K, state_slot_stride, il);
-  else if (dtype == ZK_BF16)
-    conv_decode_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, seq_slot, (bf16*)y, n_seqs,
-                                                           D, K, state_slot_stride, il);
-  else
-    return ZK_EINVAL;
-  return ZK_LAUNCH_STATUS();
+    return zk_launch_dependent(conv_decode_kernel<float>, grid, dim3(threads), 0, stream, (const float*)bcx, state, w, bias,
+                               seq_slot, (float*)y, n_seqs, D, K, state_slot_stride, il);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(conv_decode_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)bcx, state, w, bias,
+                               seq_slot, (bf16*)y, n_seqs, D, K, state_slot_stride, il);
+  return ZK_EINVAL;
 }
 
 }  // extern "C"
