@@ -110,6 +110,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
   const int slots = H + 2 * Hkv;
+  zk_let_next_start();
+  zk_wait_prior();   // qkv is the kernel before's result
   const int pos = tok_pos[t];
   float cs[E], sn[E];
 #pragma unroll
@@ -461,7 +463,7 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
   if (n_tokens >= 256 && !dense_out && (hd == 64 || hd == 128) && (!inv_freq || (n_rot == hd && !interleaved)) &&
       (dtype == ZK_F32 || dtype == ZK_BF16)) {
 #define ZK_QKP(T, HDV)                                                                                               \
-  qk_prepare_token_kernel<T, HDV><<<n_tokens, ATT_WARPS * 32, 0, stream>>>(                                          \
+  zk_launch_dependent(qk_prepare_token_kernel<T, HDV>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,             \
       (const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, \
       pt_stride, H, Hkv, eps, page_size, write_kv, status)
     if (dtype == ZK_F32 && hd == 64) ZK_QKP(float, 64);

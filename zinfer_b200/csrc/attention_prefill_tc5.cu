@@ -115,6 +115,10 @@ __global__ void __launch_bounds__(THREADS, 3)
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
   const unsigned tmem_o = tmem_base + 64;
+  // Barriers and tensor memory are set up while the kernel before this one ends; q and the cache
+  // are its results.  (The batch's index arrays read above were uploaded before the step began.)
+  zk_let_next_start();
+  zk_wait_prior();
 
   if (warp == 4 && lane == 0) {
     // ---------------------------------------------------------------- producer
@@ -366,8 +370,7 @@ int zk_attn_prefill_tc5(const void* q, const void* k_cache, const void* v_cache,
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_tiles, Hkv * (G / gp));
-  attn_prefill_tc5_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p);
-  return ZK_LAUNCH_STATUS();
+  return zk_launch_dependent(attn_prefill_tc5_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p);
 }
 
 }  // extern "C"

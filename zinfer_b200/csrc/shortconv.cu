@@ -65,6 +65,8 @@ __global__ void conv_forward_vec8_kernel(const bf16* __restrict__ bcx, const flo
                                          int K, long long state_slot_stride, int il) {
   const int ch = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const int t = blockIdx.x;
+  zk_let_next_start();
+  zk_wait_prior();   // bcx is the kernel before's result, and the state is read or written by it
   if (ch >= D || t >= n_tokens) return;
   const int b = tok_seq[t];
   const int i = t - cu_q[b];
@@ -116,6 +118,8 @@ __global__ void conv_state_update_kernel(const T* __restrict__ bcx, float* __res
                                          int D, int K, long long state_slot_stride, int il) {
   const int ch = blockIdx.y * blockDim.x + threadIdx.x;
   const int b = blockIdx.x;
+  zk_let_next_start();
+  zk_wait_prior();   // bcx is the kernel before's result, and the state is read or written by it
   if (ch >= D || b >= n_seqs) return;
   const int t0 = cu_q[b], Tq = cu_q[b + 1] - t0;
   if (Tq <= 0) return;
@@ -173,9 +177,8 @@ int zk_conv_forward(const void* bcx, const float* state, const float* w, const f
       (reinterpret_cast<uintptr_t>(bcx) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(state) |
        reinterpret_cast<uintptr_t>(w)) % 16 == 0) {
     dim3 grid8(n_tokens, ceil_div_i(D / 8, threads));
-    conv_forward_vec8_kernel<<<grid8, threads, 0, stream>>>((const bf16*)bcx, state, w, bias, tok_seq, cu_q, seq_slot,
-                                                            (bf16*)y, n_tokens, D, K, state_slot_stride, il);
-    return ZK_LAUNCH_STATUS();
+    return zk_launch_dependent(conv_forward_vec8_kernel, grid8, dim3(threads), 0, stream, (const bf16*)bcx, state, w, bias,
+                               tok_seq, cu_q, seq_slot, (bf16*)y, n_tokens, D, K, state_slot_stride, il);
   }
   dim3 grid(n_tokens, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
@@ -196,11 +199,11 @@ int zk_conv_state_update(const void* bcx, float* state, const int* cu_q, const i
   const int threads = 128;
   dim3 grid(n_seqs, ceil_div_i(D, threads));
   if (dtype == ZK_F32)
-    conv_state_update_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, state, cu_q, seq_slot, n_seqs, D,
-                                                                  K, state_slot_stride, il);
+    return zk_launch_dependent(conv_state_update_kernel<float>, grid, dim3(threads), 0, stream, (const float*)bcx, state,
+                               cu_q, seq_slot, n_seqs, D, K, state_slot_stride, il);
   else if (dtype == ZK_BF16)
-    conv_state_update_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, state, cu_q, seq_slot, n_seqs, D, K,
-                                                                 state_slot_stride, il);
+    return zk_launch_dependent(conv_state_update_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)bcx, state,
+                               cu_q, seq_slot, n_seqs, D, K, state_slot_stride, il);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
