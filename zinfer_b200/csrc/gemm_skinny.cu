@@ -129,15 +129,14 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   // much arithmetic (many tokens) or a norm prologue can hide them, else at the top of the loop;
   // measured, not derived.
   constexpr bool PIPE = NT >= 4 || NORM;
-  // The register-resident norm prologue below (up to 8 rows) holds a thread's share of the rows;
-  // the first weights are then requested after it, not before, so that the two do not add up.
+  // The short norm prologue below (up to 8 rows, K up to 8 values per thread and row).
   const bool norm_in_registers = NORM && NT == 1 && K <= WARPS * 32 * 8;
   // Weights need nothing of the kernel before: the first are requested, then the next kernel is let
   // in, then this one waits.  Measured on the LFM2-1.2B step at 8 rows: 0.712 ms in this order, 0.754
   // with the loads after zk_let_next_start(), 0.770 with zk_let_next_start() after the main loop, and
   // 0.749 when the kernels whose norm fills the registers asked for their first weights with
   // prefetch.global.L2 instead of nothing.
-  if ((PIPE && !norm_in_registers) || !PIPE) load_w(s_begin);
+  if (!norm_in_registers || RG <= 2) load_w(s_begin);
   zk_let_next_start();
   zk_wait_prior();   // the rows (X, Xf, the convolution's state) and C are the kernels' before
 
@@ -148,32 +147,47 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     float* part = row_scale + NT * 8;  // [NT * 8][WARPS] partial sums of squares
     constexpr int TH = WARPS * 32;
     if (norm_in_registers) {
-      // Up to 8 rows of up to 2 float4 per thread: every value is loaded once, all loads are under
-      // way together, and the rows stay in registers between the sum and the scaling.  A row's sum
-      // is added in the same order as below (per thread over k, over the lanes, over the warps).
-      float4 v[8][2], w[2];
+      // Up to 8 rows of up to 2 float4 per thread, four rows at a time.  The rows go to shared memory
+      // as bfloat16(x * w) WITHOUT the row's scale: the scale is one factor of the whole dot product
+      // and is applied to the float32 sum in the epilogue.  So no value has to be kept in registers
+      // until the sum of squares is known, and the first weights can be under way meanwhile.  A
+      // row's sum is added per thread over k, over the lanes, over the warps.
+      float ss[8];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) ss[m] = 0.f;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int k = threadIdx.x * 4 + j * TH * 4;
-        w[j] = k < K ? *reinterpret_cast<const float4*>(a.norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) {
+          const float4 w = *reinterpret_cast<const float4*>(a.norm_w + k);
 #pragma unroll
-        for (int m = 0; m < 8; ++m)
-          v[m][j] = (m < M && k < K) ? *reinterpret_cast<const float4*>(a.Xf + (size_t)m * a.ldx + k)
+          for (int h = 0; h < 2; ++h) {
+            float4 v[4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m)
+              v[m] = (4 * h + m < M) ? *reinterpret_cast<const float4*>(a.Xf + (size_t)(4 * h + m) * a.ldx + k)
                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              float t = ss[4 * h + m];
+              t = fmaf(v[m].x, v[m].x, t);
+              t = fmaf(v[m].y, v[m].y, t);
+              t = fmaf(v[m].z, v[m].z, t);
+              t = fmaf(v[m].w, v[m].w, t);
+              ss[4 * h + m] = t;
+              if (4 * h + m < M) {
+                uint2 pk;
+                pk.x = pack2(v[m].x * w.x, v[m].y * w.y);
+                pk.y = pack2(v[m].z * w.z, v[m].w * w.w);
+                *reinterpret_cast<uint2*>(xs + (size_t)(4 * h + m) * xs_ld + k) = pk;
+              }
+            }
+          }
+        }
       }
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          if (threadIdx.x * 4 + j * TH * 4 < K) {
-            ss = fmaf(v[m][j].x, v[m][j].x, ss);
-            ss = fmaf(v[m][j].y, v[m][j].y, ss);
-            ss = fmaf(v[m][j].z, v[m][j].z, ss);
-            ss = fmaf(v[m][j].w, v[m][j].w, ss);
-          }
-        }
-        const float t = warp_sum(ss);
+        const float t = warp_sum(ss[m]);
         if (lane == 0 && m < M) part[m * WARPS + warp] = t;
       }
       __syncthreads();
@@ -184,24 +198,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
         row_scale[threadIdx.x] = 1.0f / sqrtf(t / (float)K + a.eps);
       }
       __syncthreads();
-#pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        if (m < M) {
-          const float sc = row_scale[m];
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int k = threadIdx.x * 4 + j * TH * 4;
-            if (k < K) {
-              uint2 pk;
-              pk.x = pack2((v[m][j].x * sc) * w[j].x, (v[m][j].y * sc) * w[j].y);
-              pk.y = pack2((v[m][j].z * sc) * w[j].z, (v[m][j].w * sc) * w[j].w);
-              *reinterpret_cast<uint2*>(xs + (size_t)m * xs_ld + k) = pk;
-            }
-          }
-        }
-      }
-      __syncthreads();
-      load_w(s_begin);
+      if (RG > 2) load_w(s_begin);   // (the narrower kernels asked for theirs before they waited; these have no room)
     } else {
     for (int m0 = 0; m0 < M; m0 += 4) {
       float ss[4] = {0.f, 0.f, 0.f, 0.f};
@@ -323,6 +320,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) v += red[w][row][m];
+    if (NORM && norm_in_registers) v *= row_scale[m];   // the rows were staged without their scale
     return v;
   };
 
