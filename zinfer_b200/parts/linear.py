@@ -59,9 +59,10 @@ def as_tensor(a: Union[torch.Tensor, NormedRows]) -> torch.Tensor:
 # A block that applies the norm itself reads all M rows again, so fusing the norm pays only while
 # few blocks do so (about one per SM) or the rows are very few; measured on the LFM2-1.2B shapes:
 # fused 12.5 us against 14.5 us for the short convolution's in_proj (128 blocks, 8 rows), but
-# 75 us against 50 us for the head (2048 blocks).
+# 75 us against 50 us for the head (2048 blocks).  A whole step with every norm fused against the
+# rule below: 0.673 against 0.680 ms at 4 rows, 0.723 against 0.714 ms at 8 rows.
 NORM_FUSION_MAX_BLOCKS = 160
-NORM_FUSION_ANY_BLOCKS_ROWS = 2
+NORM_FUSION_ANY_BLOCKS_ROWS = 4
 
 
 def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_rows: bool = False,
