@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   // with the loads after zk_let_next_start(), 0.770 with zk_let_next_start() after the main loop, and
   // 0.749 when the kernels whose norm fills the registers asked for their first weights with
   // prefetch.global.L2 instead of nothing.
-  if (!norm_in_registers || RG <= 2) load_w(s_begin);
+  load_w(s_begin);
   zk_let_next_start();
   zk_wait_prior();   // the rows (X, Xf, the convolution's state) and C are the kernels' before
 
@@ -198,7 +198,6 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
         row_scale[threadIdx.x] = 1.0f / sqrtf(t / (float)K + a.eps);
       }
       __syncthreads();
-      if (RG > 2) load_w(s_begin);   // (the narrower kernels asked for theirs before they waited; these have no room)
     } else {
     for (int m0 = 0; m0 < M; m0 += 4) {
       float ss[4] = {0.f, 0.f, 0.f, 0.f};
