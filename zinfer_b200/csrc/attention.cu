@@ -350,6 +350,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   T* __restrict__ out, int n_rows, int hd, int num_splits) {
+  zk_let_next_start();
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
