@@ -664,3 +664,48 @@ def test_tcgen05_prompt_attention_far_key_and_continued_prompt(k, H, Hkv, page):
         assert torch.allclose(out[t].float().cpu().reshape(H, hd), winner, atol=0.05), f"query {t} did not pick the far key"
     assert torch.allclose(out2[-1].float().cpu().reshape(H, hd), winner, atol=0.05)
     assert not torch.allclose(out[far - 1].float().cpu().reshape(H, hd), winner, atol=0.05), "a later key was seen"
+
+
+# ------------------------------------------------------------------------------- dependent launches
+
+@pytest.mark.parametrize("rows", [1, 8, 40, 300])
+def test_dependent_launches_keep_the_order_of_a_chain(k, rows):
+    """The kernels of a step start while the kernel before them still runs and wait for it by
+    themselves.  A chain in which every kernel reads what the one before wrote and overwrites what the
+    one before read (norm -> contraction with a fused norm -> contraction that adds into the stream),
+    launched back to back, gives the same bits as the chain with the device drained after every
+    kernel, where nothing can overlap; 1 and 8 rows take the few-row kernels, 40 the tcgen05 kernel
+    for few rows, 300 the persistent pairs with their TMA reduce-add."""
+    from zinfer_b200.parts.linear import NormedRows, linear
+    D, F, eps = 1024, 2048, 1e-5
+    up = rnd((F, D), 61, torch.bfloat16, 0.03).cuda()
+    down = rnd((D, F), 62, torch.bfloat16, 0.03).cuda()
+    nw = (1.0 + rnd((D,), 63, torch.float32, 0.1)).cuda()
+    x0 = rnd((rows, D), 64, torch.float32).cuda()
+
+    def chain(drain):
+        x = x0.clone()
+        torch.cuda.synchronize()
+        for _ in range(24):
+            h = linear(NormedRows(x, nw, eps, torch.bfloat16), up)       # reads x
+            if drain:
+                torch.cuda.synchronize()
+            linear(h, down, out=x, accumulate=True)                      # writes x, which the kernel before read
+            if drain:
+                torch.cuda.synchronize()
+            xn = k.rmsnorm(x, nw, eps, torch.bfloat16)                   # reads x again
+            if drain:
+                torch.cuda.synchronize()
+            linear(xn, up, out=h)                                        # overwrites h, which a kernel before read
+            if drain:
+                torch.cuda.synchronize()
+            linear(h, down, out=x, accumulate=True)
+            if drain:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return x
+
+    a, b = chain(False), chain(True)
+    assert torch.isfinite(a).all() and a.abs().max() > 0
+    assert torch.equal(a, b)
+    assert k.status_word("cuda").item() == 0
