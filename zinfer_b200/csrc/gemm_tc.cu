@@ -17,6 +17,10 @@
 //            partial tile in its own shared memory, and after a cluster barrier every block adds
 //            the partials of its share of the tokens in split order, reading the other blocks'
 //            shared memory directly (no workspace, no atomics, the same bits each run).
+// Products of more than 64 rows with N a multiple of 256 take the persistent form further down
+// (one block, or a pair of blocks with tcgen05.mma.cta_group::2, per SM walking 256-wide tiles, a
+// TMA-store epilogue).  Every kernel here is launched as a dependent launch: the producer requests
+// the weight tiles of its first stages before it waits for the kernel before this one.
 // Accumulation is float32 in tensor memory.  (Reference: the matmul driver with its accumulate
 // flag, src/model.zig:903-1026, 918-920.)
 //
@@ -786,6 +790,8 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   if (!make_map(&ma, W, N, K, ldw, BM) || !make_map(&mb, X, M, K, ldx, bn)) return ZK_EINVAL;
   dim3 grid(ceil_div_i(N, BM), 1, splits);
+  // four stages: measured on whole steps of 16 / 64 sequences 1.09 / 1.40 ms, with three stages 1.12 / 1.48,
+  // with eight 1.18 / 1.72
 #define ZK_TC_SWAP(BNV)                                                                     \
   return f32 ? launch<BNV, 4, true, float>(ma, mb, p, grid, stream) : launch<BNV, 4, true, bf16>(ma, mb, p, grid, stream);
   if (bn == 16) { ZK_TC_SWAP(16) }
