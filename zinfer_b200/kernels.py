@@ -275,7 +275,9 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
             accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1,
             swiglu: bool = False) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
-    More than 64 rows: 128 x 128 tiles of tokens x weight rows.  Up to 64 rows: the weights take
+    More than 64 rows: persistent blocks on 256-wide tiles when N is a multiple of 256 (pairs of
+    blocks with tcgen05.mma.cta_group::2 above 128 rows, TMA stores), else one 128 x 128 tile of
+    tokens x weight rows per block.  Up to 64 rows: the weights take
     the 128-row side and K is cut into `splits` (1, 2, 4 or 8) parts, one per block of a cluster,
     that are added in order.  With `swiglu` (not with split K) w holds groups of 16 gate rows and
     their 16 up rows and the result is silu(gate) * up, [M, N/2]."""
