@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   // measured, not derived.
   constexpr bool PIPE = NT >= 4 || NORM;
   // The short norm prologue below (up to 8 rows, K up to 8 values per thread and row).
-  const bool norm_in_registers = NORM && NT == 1 && K <= WARPS * 32 * 8;
+  const bool norm_one_pass = NORM && NT == 1 && K <= WARPS * 32 * 8;
   // Weights need nothing of the kernel before: the first are requested, then the next kernel is let
   // in, then this one waits.  Measured on the LFM2-1.2B step at 8 rows: 0.712 ms in this order, 0.754
   // with the loads after zk_let_next_start(), 0.770 with zk_let_next_start() after the main loop, and
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   if constexpr (NORM) {
     float* part = row_scale + NT * 8;  // [NT * 8][WARPS] partial sums of squares
     constexpr int TH = WARPS * 32;
-    if (norm_in_registers) {
+    if (norm_one_pass) {
       // Up to 8 rows of up to 2 float4 per thread, four rows at a time.  The rows go to shared memory
       // as bfloat16(x * w) WITHOUT the row's scale: the scale is one factor of the whole dot product
       // and is applied to the float32 sum in the epilogue.  So no value has to be kept in registers
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) v += red[w][row][m];
-    if (NORM && norm_in_registers) v *= row_scale[m];   // the rows were staged without their scale
+    if (NORM && norm_one_pass) v *= row_scale[m];   // the rows were staged without their scale
     return v;
   };
 
