@@ -74,6 +74,22 @@ def test_attention_against_loops_with_window_and_groups():
             assert np.allclose(wo @ np.concatenate(heads), got[t], atol=1e-12)
 
 
+def test_attention_takes_another_position_encoding_in_the_place_of_the_rotation():
+    """The `encode` hook runs where the rotation runs: given the rotation itself it reproduces the
+    built-in path, and given nothing the scores are position-free."""
+    T, D, H, Hkv, hd = 6, 8, 2, 1, 4
+    xn = rnd((T, D), 30)
+    wq, wk, wv, wo = rnd((H * hd, D), 31, 0.3), rnd((Hkv * hd, D), 32, 0.3), rnd((Hkv * hd, D), 33, 0.3), rnd((D, H * hd), 34, 0.3)
+    qn, kn = 1 + rnd((hd,), 35, 0.1), 1 + rnd((hd,), 36, 0.1)
+    f = P.rope_inv_freq(50.0, hd)
+    built_in = P.gqa_attention(xn, wq, wk, wv, wo, qn, kn, H, Hkv, hd, 1e-6, f, dtype=np.float64)
+    rotate = lambda q, k, pos: (P.apply_rope(q, pos, f, np.float64), P.apply_rope(k, pos, f, np.float64))
+    hooked = P.gqa_attention(xn, wq, wk, wv, wo, qn, kn, H, Hkv, hd, 1e-6, None, dtype=np.float64, encode=rotate)
+    assert np.array_equal(built_in, hooked)
+    bare = P.gqa_attention(xn, wq, wk, wv, wo, qn, kn, H, Hkv, hd, 1e-6, None, dtype=np.float64)
+    assert not np.allclose(bare, built_in)
+
+
 def test_swiglu_against_scalars():
     xn, w1, w3, w2 = rnd((2, 5), 17), rnd((7, 5), 18), rnd((7, 5), 19), rnd((5, 7), 20)
     got = P.swiglu(xn, w1, w3, w2, np.float64)
