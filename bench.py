@@ -52,6 +52,7 @@ SECONDARY = {
 CONTEXT = 4096
 PROMPT_RANGE = (512, 2048)
 PREFILL_TOKENS = 2048
+POINT_STEPS = 64            # the batch-1 and batch-64 points are timed over at least this many steps
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -129,29 +130,12 @@ def model_numbers(cfg, n_layers_run: int) -> dict:
             "kv_bytes_per_token": n_attn * 2 * KV * 2, "conv_state_bytes": (len(kinds) - n_attn) * (cfg.conv_L_cache - 1) * D * 4}
 
 
-def print_op_trace(engine, batch: int) -> None:
-    """Where block 0 of the persistent single-token kernel spends a step, by kind of operation."""
-    plan = engine._fused[batch].plan
-    if not plan:
-        print("the model's single-token step is not fused", file=sys.stderr)
-        return
-    kinds: dict = {}
-    for row in plan.trace(engine.last_fused_ctx):
-        k = kinds.setdefault(row["op"], [0, 0.0, 0.0, 0.0])
-        k[0] += 1
-        for i, name in enumerate(("stage_us", "work_us", "barrier_us")):
-            k[i + 1] += row[name]
-    print(f"{'operation':28s} count  stage   work  barrier  (mean us)    sum us", file=sys.stderr)
-    for name, (n, a, b, c) in kinds.items():
-        print(f"{name:28s} {n:5d} {a / n:6.2f} {b / n:6.2f} {c / n:8.2f} {a + b + c:19.1f}", file=sys.stderr)
-    engine.status.zero_()
-
-
-def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int, trace_ops: bool = False,
-                prompt_range=None):
+def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: int, prompt_range=None):
     """Prefills `batch` prompts of lengths uniform in `prompt_range` (default PROMPT_RANGE), then times
-    `steps` decode steps.
-    Returns (ms per step, total cached tokens at the middle of the timed region, launches per step)."""
+    `steps` decode steps.  Every CUDA graph the timed steps replay is recorded before the timing
+    starts; `captures` counts the steps that had to record one all the same (expected: 0).
+    Returns (ms per step, total cached tokens at the middle of the timed region, launches per step,
+    captures)."""
     from zinfer_b200 import kernels
     lo, hi = prompt_range or PROMPT_RANGE
     lens = rng.integers(lo, hi + 1, size=batch).tolist()
@@ -166,7 +150,10 @@ def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: 
             engine.decode(slots, toks[i].tolist())
             if launches is None:
                 launches = kernels.launch_count - before
+        longest = max(lens) + warmup
+        engine.prepare_decode(batch, longest, longest + steps + 1)
         torch.cuda.synchronize()
+        captures = engine.graph_captures
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for i in range(warmup, warmup + steps):
@@ -176,11 +163,10 @@ def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: 
         engine.check_status()
         ms = start.elapsed_time(stop) / steps
         cached = sum(lens) + batch * (warmup + steps // 2)
-        if trace_ops and engine.last_fused_ctx is not None:
-            print_op_trace(engine, batch)
+        captures = engine.graph_captures - captures
     finally:
         engine.finish(slots)
-    return ms, cached, launches
+    return ms, cached, launches, captures
 
 
 def time_prefill(engine, torch, rng, cfg, warmup: int, num: dict, pk: dict) -> dict:
@@ -226,8 +212,8 @@ def secondary_arm(args) -> dict:
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     with ClockSampler() as clocks:
-        ms, cached, launches = time_decode(engine, torch, rng, batch, steps, args.warmup, cfg.vocab_size,
-                                           prompt_range=prompt_range)
+        ms, cached, launches, captures = time_decode(engine, torch, rng, batch, steps, args.warmup, cfg.vocab_size,
+                                                     prompt_range=prompt_range)
     wall = time.perf_counter() - t0
     weight_bytes = 2 * (num["layer_params"] + num["head_params"])
     step_bytes = weight_bytes + cached * num["kv_bytes_per_token"] + batch * num["conv_state_bytes"] * 2
@@ -242,7 +228,7 @@ def secondary_arm(args) -> dict:
                          "frac": round(achieved / pk["hbm_gbs"], 4), "weight_gb": round(weight_bytes / 1e9, 3),
                          "cache_gb": round(cached * num["kv_bytes_per_token"] / 1e9, 3)},
             "clocks": clocks.summary(), "gpu_launches": int(launches or 0) * steps,
-            "wall_s_with_prompts": round(wall, 1)}
+            "graph_captures_in_timed_steps": captures, "wall_s_with_prompts": round(wall, 1)}
 
 
 def own_arm(args) -> dict:
@@ -264,7 +250,7 @@ def own_arm(args) -> dict:
     model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True)
     B = args.batch
     engine = z.Engine(model, max_batch=64, max_seq_len=CONTEXT, max_tokens=64 * CONTEXT, page_size=64,
-                      use_graphs=not args.no_graphs, fused_decode=args.fused)
+                      use_graphs=not args.no_graphs)
     if args.only == "prefill":
         return {"prefill": time_prefill(engine, torch, np.random.default_rng(0), cfg, args.warmup,
                                         model_numbers(cfg, cfg.num_hidden_layers), pk)}
@@ -274,8 +260,7 @@ def own_arm(args) -> dict:
 
     # decode at the headline batch, device-timed, with the clocks sampled meanwhile
     with ClockSampler() as clocks:
-        ms, cached, launches = time_decode(engine, torch, rng, B, args.steps, args.warmup, cfg.vocab_size,
-                                           trace_ops=args.trace_ops)
+        ms, cached, launches, captures = time_decode(engine, torch, rng, B, args.steps, args.warmup, cfg.vocab_size)
     value = B / (ms * 1e-3)
     step_bytes = weight_bytes + cached * num["kv_bytes_per_token"] + B * num["conv_state_bytes"] * 2
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -284,11 +269,15 @@ def own_arm(args) -> dict:
         return {"value": round(value, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches,
                 "roofline_frac": round(achieved / pk["hbm_gbs"], 4)}
 
-    # other batch sizes
+    # other batch sizes, each over at least POINT_STEPS steps whatever --steps says
     points = {}
     for b in (1, 64):
-        pms, _, _ = time_decode(engine, torch, rng, b, max(8, args.steps // 2), args.warmup, cfg.vocab_size)
+        pms, pcached, _, pcap = time_decode(engine, torch, rng, b, max(POINT_STEPS, args.steps), args.warmup,
+                                            cfg.vocab_size)
+        captures += pcap
+        pbytes = weight_bytes + pcached * num["kv_bytes_per_token"] + b * num["conv_state_bytes"] * 2
         points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+        points[f"decode_b{b}_hbm_frac"] = round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     prefill = time_prefill(engine, torch, rng, cfg, args.warmup, num, pk)
     T = PREFILL_TOKENS
@@ -321,6 +310,7 @@ def own_arm(args) -> dict:
         "clocks": clocks.summary(),
         "e2e": e2e,
         "gpu_launches": int(launches or 0) * args.steps,
+        "graph_captures_in_timed_steps": captures,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
@@ -341,9 +331,6 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--model", default="1.2b", choices=["1.2b"] + sorted(SECONDARY),
                     help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only)")
-    ap.add_argument("--trace-ops", action="store_true",
-                    help="with --fused --only decode: print where block 0 of the persistent kernel spends a step")
-    ap.add_argument("--fused", action="store_true", help="run decode steps of up to 16 sequences as one persistent kernel")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -5,7 +5,15 @@ kind, head counts and group size, head size, feed-forward rule, conv window and 
 base, eps, tied or untied head, norm-weight init, vocabulary); tiny_c adds a windowed
 attention group next to a full one, a width and vocabulary that are no power of two, a
 two-tap convolution and a float32 weight file; tiny_d and tiny_e have the head size 64 that the
-tensor-core attention and the one-kernel single-token step take, and differ in the rest.
+tensor-core attention kernels take, and differ in the rest.
+
+Each of them comes a second time as loud_a ... loud_e: the same sizes with weights N(0, 1/hidden)
+and norm weights 1 + N.  With the standard deviation 0.02 that the tiny configurations are
+specified with, a contraction over 64 to 256 inputs shrinks its input some tenfold, so that the
+logits are the token's own embedding plus small corrections, and a fault in a mixer moves them by
+less than the bfloat16 tolerance.  In the loud variants every contraction keeps the size of its
+input, every layer changes the residual stream by as much as it holds, and a wrong mixer output,
+cache slot or state row changes the logits as a whole.
 """
 from __future__ import annotations
 
@@ -68,13 +76,21 @@ TINY = {
 }
 
 
+for _name in list(TINY):
+    _spec = TINY[_name]
+    TINY["loud_" + _name[-1]] = dict(_spec, seed=_spec["seed"] + 100, norm_init="one_plus_normal",
+                                     std=float(_spec["config"]["hidden_size"]) ** -0.5)
+QUIET = [n for n in TINY if n.startswith("tiny_")]
+LOUD = [n for n in TINY if n.startswith("loud_")]
+
+
 def make_model_folder(folder, name: str) -> Path:
     import torch
     import zinfer_b200 as z
 
     spec = TINY[name]
     cfg = z.config_from_dict(spec["config"])
-    return z.write_random_model(folder, cfg, spec["seed"], norm_init=spec["norm_init"],
+    return z.write_random_model(folder, cfg, spec["seed"], std=spec.get("std", 0.02), norm_init=spec["norm_init"],
                                 storage_dtype=getattr(torch, spec["storage"]))
 
 
@@ -89,8 +105,20 @@ def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
     return float(np.max(np.abs(got.astype(np.float64) - ref.astype(np.float64)))) / scale
 
 
-# tolerances, relative to max |logit| of the plain implementation
+# Tolerances: largest absolute error relative to max |logit| of the plain float64 implementation.
+# TOL holds for the tiny_* configurations as specified (weights N(0, 0.02)).  The loud variants,
+# and any model whose contractions keep the size of their input (the LFM2-1.2B shape with
+# N(0, 0.02) at width 2048 is one), have a higher floor in bfloat16: rounding nothing but the
+# inputs of the contractions, the cache and the probabilities to bfloat16, with exact
+# arithmetic otherwise, already gives 1.2e-2 to 2.8e-2 (test_plain.py measures it with
+# PlainLfm2(round_activations=...)), most of it from the normalised rows that enter every
+# contraction.  A wrong row, slot, chunk or state moves these models' logits by 0.3 or more.
 TOL = {"float32": 5e-5, "bfloat16": 2e-2}
+TOL_LOUD = {"float32": 5e-5, "bfloat16": 4e-2}
+
+
+def tol(name: str, dtype: str) -> float:
+    return (TOL_LOUD if name.startswith("loud_") else TOL)[dtype]
 
 
 def run_trace(model_dir, dtype: str, steps: list[dict], max_tokens: int, out_dir) -> dict[int, np.ndarray]:

@@ -13,6 +13,11 @@ Deliberate differences from zinfer's arithmetic, both making this file more exac
 (src/ffn.zig:12-28) and no softmax tile is skipped (src/attention.zig:493).
 
 Everything is computed in `dtype` (float32 by default, float64 on request).
+
+`act` (a function, usually `to_bf16`) makes the parts round what a reduced-precision pipeline
+has to round even with exact arithmetic: the inputs and outputs of the contractions, what goes
+into the cache, and the probabilities.  It measures the error floor of such a pipeline; no
+comparison with the engine uses it as the expected value.
 """
 from __future__ import annotations
 
@@ -135,7 +140,11 @@ def apply_rope(x: np.ndarray, positions: np.ndarray, inv_freq: np.ndarray, dtype
     return out
 
 
-def short_conv(xn, w_in, conv_w, w_out, conv_b=None, b_in=None, b_out=None, dtype=np.float32):
+def _act(act, x, dtype):
+    return x if act is None else act(np.asarray(x, dtype=np.float32)).astype(dtype)
+
+
+def short_conv(xn, w_in, conv_w, w_out, conv_b=None, b_in=None, b_out=None, dtype=np.float32, act=None):
     """Gated short convolution of a whole sequence starting from a zero state
     (src/model.zig:1994-2028): [B, C, X] = xn W_in^T; u = B*X;
     c_t = sum_k w[:, k] u_{t-(K-1)+k} (tap K-1 on the current token); y = C*c; y W_out^T.
@@ -145,6 +154,7 @@ def short_conv(xn, w_in, conv_w, w_out, conv_b=None, b_in=None, b_out=None, dtyp
     bcx = xn.astype(dtype) @ w_in.astype(dtype).T
     if b_in is not None:
         bcx = bcx + b_in.astype(dtype)
+    bcx = _act(act, bcx, dtype)
     Bg, Cg, X = bcx[:, :D], bcx[:, D:2 * D], bcx[:, 2 * D:]
     u = Bg * X
     hist = np.concatenate([np.zeros((K - 1, D), dtype=dtype), u], axis=0)
@@ -153,7 +163,7 @@ def short_conv(xn, w_in, conv_w, w_out, conv_b=None, b_in=None, b_out=None, dtyp
         c = c + conv_w[:, k].astype(dtype)[None, :] * hist[k:k + T]
     if conv_b is not None:
         c = c + conv_b.astype(dtype)[None, :]
-    y = Cg * c
+    y = _act(act, Cg * c, dtype)
     out = y @ w_out.astype(dtype).T
     if b_out is not None:
         out = out + b_out.astype(dtype)
@@ -161,7 +171,7 @@ def short_conv(xn, w_in, conv_w, w_out, conv_b=None, b_in=None, b_out=None, dtyp
 
 
 def gqa_attention(xn, wq, wk, wv, wo, q_norm_w, k_norm_w, n_heads, n_kv, hd, eps, inv_freq,
-                  window=0, dtype=np.float32, cache_round=None, encode=None):
+                  window=0, dtype=np.float32, cache_round=None, encode=None, act=None):
     """Grouped-query attention over a whole sequence (src/model.zig:1715-1991):
     q,k,v projections; per-head RMSNorm of q and k with the layer eps
     (src/model.zig:1741-1744, 1760-1763); RoPE; causal scores (q.k)*1/sqrt(hd)
@@ -172,9 +182,11 @@ def gqa_attention(xn, wq, wk, wv, wo, q_norm_w, k_norm_w, n_heads, n_kv, hd, eps
     where the rotation runs; tests of parts that are not the reference's use it."""
     T, _ = xn.shape
     xn = xn.astype(dtype)
-    q = (xn @ wq.astype(dtype).T).reshape(T, n_heads, hd)
-    k = (xn @ wk.astype(dtype).T).reshape(T, n_kv, hd)
-    v = (xn @ wv.astype(dtype).T).reshape(T, n_kv, hd)
+    q = _act(act, xn @ wq.astype(dtype).T, dtype).reshape(T, n_heads, hd)
+    k = _act(act, xn @ wk.astype(dtype).T, dtype).reshape(T, n_kv, hd)
+    v = _act(act, xn @ wv.astype(dtype).T, dtype).reshape(T, n_kv, hd)
+    if act is not None and cache_round is None:
+        cache_round = act
     pos = np.arange(T)
     if q_norm_w is not None:
         q = rms_norm(q, q_norm_w, eps, dtype)
@@ -200,18 +212,17 @@ def gqa_attention(xn, wq, wk, wv, wo, q_norm_w, k_norm_w, n_heads, n_kv, hd, eps
         s = np.where(mask, s, -np.inf)
         m = np.max(s, axis=-1, keepdims=True)
         p = np.exp(s - m)
-        p = p / np.sum(p, axis=-1, keepdims=True)
-        out[:, h, :] = p @ v[:, kh, :]
-    return (out.reshape(T, n_heads * hd) @ wo.astype(dtype).T).astype(dtype)
+        out[:, h, :] = (_act(act, p, dtype) @ v[:, kh, :]) / np.sum(p, axis=-1, keepdims=True)
+    return (_act(act, out.reshape(T, n_heads * hd), dtype) @ wo.astype(dtype).T).astype(dtype)
 
 
-def swiglu(xn, w1, w3, w2, dtype=np.float32):
+def swiglu(xn, w1, w3, w2, dtype=np.float32, act=None):
     """h = silu(xn W1^T) * (xn W3^T); out = h W2^T; silu(g) = g / (1 + exp(-g))
     (src/model.zig:1085-1117, 2411-2422; src/ffn.zig:31-33, 49-57)."""
     xn = xn.astype(dtype)
     g = xn @ w1.astype(dtype).T
     u = xn @ w3.astype(dtype).T
-    h = g / (dtype(1.0) + np.exp(-g)) * u
+    h = _act(act, g / (dtype(1.0) + np.exp(-g)) * u, dtype)
     return (h @ w2.astype(dtype).T).astype(dtype)
 
 
@@ -220,13 +231,14 @@ def swiglu(xn, w1, w3, w2, dtype=np.float32):
 class PlainLfm2:
     """Whole-sequence LFM2 forward from a model folder (config.json + model.safetensors)."""
 
-    def __init__(self, folder, dtype=np.float32, round_weights_bf16=False):
+    def __init__(self, folder, dtype=np.float32, round_weights_bf16=False, round_activations=None):
         folder = Path(folder)
         self.cfg = json.loads((folder / "config.json").read_text())
         self.w = read_safetensors(folder / "model.safetensors")
         if round_weights_bf16:
             self.w = {k: (to_bf16(v) if v.dtype == np.float32 and v.ndim >= 2 else v) for k, v in self.w.items()}
         self.dtype = dtype
+        self.act = round_activations
         c = self.cfg
         self.D = int(c["hidden_size"])
         self.H = int(c["num_attention_heads"])
@@ -242,25 +254,25 @@ class PlainLfm2:
         """x += Mixer(RMSNorm(x, operator_norm)); x += FFN(RMSNorm(x, ffn_norm))
         (src/model.zig:2395-2422)."""
         w, dt, p = self.w, self.dtype, f"model.layers.{i}."
-        xn = rms_norm(x, w[p + "operator_norm.weight"], self.eps, dt)
+        xn = _act(self.act, rms_norm(x, w[p + "operator_norm.weight"], self.eps, dt), dt)
         kind = self.kinds[i]
         if kind == "conv":
             cw = w[p + "conv.conv.weight"]
             cw = cw.reshape(cw.shape[0], cw.shape[-1])
             y = short_conv(xn, w[p + "conv.in_proj.weight"], cw, w[p + "conv.out_proj.weight"],
                            conv_b=w.get(p + "conv.conv.bias"), b_in=w.get(p + "conv.in_proj.bias"),
-                           b_out=w.get(p + "conv.out_proj.bias"), dtype=dt)
+                           b_out=w.get(p + "conv.out_proj.bias"), dtype=dt, act=self.act)
         else:
             y = gqa_attention(xn, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"],
                               w[p + "self_attn.v_proj.weight"], w[p + "self_attn.out_proj.weight"],
                               w[p + "self_attn.q_layernorm.weight"], w[p + "self_attn.k_layernorm.weight"],
                               self.H, self.Hkv, self.hd, self.eps, self.inv_freq,
                               window=self.window if kind == "sliding_attention" else 0,
-                              dtype=dt, cache_round=cache_round)
+                              dtype=dt, cache_round=cache_round, act=self.act)
         x = x + y
-        xn = rms_norm(x, w[p + "ffn_norm.weight"], self.eps, dt)
+        xn = _act(self.act, rms_norm(x, w[p + "ffn_norm.weight"], self.eps, dt), dt)
         x = x + swiglu(xn, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
-                       w[p + "feed_forward.w2.weight"], dt)
+                       w[p + "feed_forward.w2.weight"], dt, act=self.act)
         return x
 
     def hidden(self, tokens, cache_round=None):
@@ -274,7 +286,7 @@ class PlainLfm2:
         (src/model.zig:599-600, 2484-2486); the head is lm_head or the tied embedding
         (src/model.zig:595-598, 2490)."""
         x = self.hidden(tokens, cache_round)
-        xn = rms_norm(x, self.w["model.embedding_norm.weight"], self.eps, self.dtype)
+        xn = _act(self.act, rms_norm(x, self.w["model.embedding_norm.weight"], self.eps, self.dtype), self.dtype)
         head = self.w["model.embed_tokens.weight"] if self.tied else self.w["lm_head.weight"]
         return (xn @ head.astype(self.dtype).T).astype(np.float32)
 

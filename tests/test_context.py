@@ -1,10 +1,12 @@
 """The step's batch description on the host: how sequences of unequal lengths are packed into one
-int32 buffer, how query tiles are cut, and how a single-token step cuts the keys into chunks."""
+int32 buffer; and the attention part's launch plans: how query tiles are cut, and how a
+single-token step cuts the keys into chunks."""
 import numpy as np
 import pytest
 import torch
 
-from zinfer_b200.engine.context import StepContext, attn_tiles_host, batch_layout, pack_batch
+from zinfer_b200.engine.context import StepContext, batch_layout, pack_batch
+from zinfer_b200.parts.attention import key_capacity, key_chunks, query_tiles
 
 
 def unpack(buf, n_tokens, n_seqs):
@@ -35,7 +37,7 @@ def test_packed_batch_holds_every_sequence_at_its_place(lens):
 
 @pytest.mark.parametrize("lens,bq", [([5, 1, 9, 2], 4), ([128, 1, 200], 128), ([3], 16), ([64, 64], 32)])
 def test_query_tiles_cover_every_token_once(lens, bq):
-    tiles = attn_tiles_host(lens, bq)
+    tiles = query_tiles(lens, bq)
     assert tiles.dtype == np.int32 and tiles.shape[0] == 2
     seen = [np.zeros(n, dtype=int) for n in lens]
     for b, q0 in tiles.T:
@@ -46,40 +48,52 @@ def test_query_tiles_cover_every_token_once(lens, bq):
     assert order == sorted(order), "tiles go sequence by sequence, front to back"
 
 
-def context(lens, starts, split_keys=0):
+def context(lens, starts):
     buf = torch.from_numpy(pack_batch(list(range(len(lens))), starts, [[0] * n for n in lens]))
     status = torch.zeros(1, dtype=torch.int32)
     return StepContext(torch.float32, torch.device("cpu"), status, buf, sum(lens), len(lens), lens,
-                       max(s + n for s, n in zip(starts, lens)), split_keys)
+                       max(s + n for s, n in zip(starts, lens)))
 
 
 def test_step_context_views_and_kind_of_step():
     ctx = context([4, 1, 2], [10, 0, 7])
     assert ctx.n_tokens == 7 and ctx.n_seqs == 3 and ctx.max_q_len == 4 and ctx.max_kv_len == 14
-    assert not ctx.is_decode and ctx.kv_splits(2) == (1, 0)
+    assert not ctx.is_decode
     assert ctx.cu_q.tolist() == [0, 4, 5, 7] and ctx.tok_pos.tolist() == [10, 11, 12, 13, 0, 7, 8]
-    seq, q0 = ctx.attn_tiles(2)
-    assert seq.tolist() == [0, 0, 1, 2] and q0.tolist() == [0, 2, 0, 0]
-    assert ctx.attn_tiles(2)[0] is seq, "tile tables are made once per tile size"
+    made = []
+    first = ctx.memo("k", lambda: made.append(1) or [1, 2])
+    assert ctx.memo("k", lambda: made.append(1) or [3]) is first and made == [1], "a memo is made once per key"
     one = context([1, 1], [5, 900])
     assert one.is_decode
     mixed = context([1, 2], [5, 9])
     assert not mixed.is_decode, "one token each is what makes a single-token step"
 
 
+def test_key_capacity_grows_in_few_coarse_steps():
+    caps = sorted({key_capacity(n) for n in range(1, 40000, 7)})
+    assert caps[:6] == [512, 768, 1024, 1536, 2048, 3072] and len(caps) <= 14
+    for n in (1, 512, 513, 3000, 32768, 32769):
+        c = key_capacity(n)
+        assert c >= n and (n <= 512 or c < 1.5 * n + 1), "never less than the sequence, never 1.5 times more"
+
+
+@pytest.mark.parametrize("sm_count", [148, 20])
 @pytest.mark.parametrize("n_seqs,n_kv,longest", [(1, 8, 100), (1, 8, 4096), (8, 8, 4096), (64, 8, 32768), (3, 1, 70000)])
-def test_key_chunks_of_a_single_token_step(n_seqs, n_kv, longest):
-    ctx = context([1] * n_seqs, [longest - 1] + [0] * (n_seqs - 1))
-    n, keys = ctx.kv_splits(n_kv)
+def test_key_chunks_of_a_single_token_step(n_seqs, n_kv, longest, sm_count):
+    n, keys = key_chunks(n_seqs, n_kv, longest, sm_count)
+    cap = key_capacity(longest)
     if n == 1:
-        assert keys == 0 and longest <= 128
+        assert keys == 0
         return
     assert keys % 64 == 0 and 128 <= keys <= 4096
-    assert (n - 1) * keys < longest <= n * keys, "the chunks cover the longest sequence, none is empty"
+    assert (n - 1) * keys < cap <= n * keys, "the chunks cover the capacity that holds the longest sequence"
+    # the plan is the same for every length that shares the capacity: a recorded step stays valid
+    assert key_chunks(n_seqs, n_kv, cap, sm_count) == (n, keys)
+    below = cap * 3 // 4 if cap & (cap - 1) == 0 else cap * 2 // 3      # the capacity before this one
+    assert key_capacity(below + 1) == cap and key_chunks(n_seqs, n_kv, below + 1, sm_count) == (n, keys)
 
 
 def test_given_chunk_size_is_kept_whatever_the_batch():
     for n_seqs in (1, 5, 40):
-        ctx = context([1] * n_seqs, [999] + [3] * (n_seqs - 1), split_keys=256)
-        assert ctx.kv_splits(4) == (4, 256)
-    assert context([1], [99], split_keys=256).kv_splits(4) == (1, 0)
+        assert key_chunks(n_seqs, 4, 1000, 148, split_keys=256) == (4, 256)
+    assert key_chunks(1, 4, 100, 148, split_keys=512) == (1, 0)

@@ -422,7 +422,7 @@ class PagedSetup:
 def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
     """Prompt step of unequal lengths into NaN-filled shuffled pages, then a single-token step
     with and without key splits, against whole-sequence references."""
-    from zinfer_b200.engine.context import attn_tiles_host
+    from zinfer_b200.parts.attention import query_tiles as attn_tiles_host
     lens = [1, 2, 37, 70, 5]
     slots = [3, 0, 5, 1, 4]
     eps = 1e-5
@@ -500,7 +500,7 @@ def test_qk_prepare_then_attention(k, dtype, H, Hkv, hd, page, n_rot, inter):
 def test_attention_far_key_and_window_edge(k, dtype, window):
     """One key among hundreds is made to win the softmax; with a window the winner sits exactly
     on the window's first position for one query and one position outside it for the next."""
-    from zinfer_b200.engine.context import attn_tiles_host
+    from zinfer_b200.parts.attention import query_tiles as attn_tiles_host
     H, Hkv, hd, page = 4, 2, 32, 32
     T = 300
     scale = 1 / math.sqrt(hd)
@@ -618,7 +618,7 @@ def test_tcgen05_prompt_attention_far_key_and_continued_prompt(k, H, Hkv, page):
     500 and ends in the middle of a key tile), with one far key that must win for every query
     that sees it, NaN in every cache row that no token has written, and a second short sequence
     in the same batch."""
-    from zinfer_b200.engine.context import attn_tiles_host
+    from zinfer_b200.parts.attention import query_tiles as attn_tiles_host
     dtype, hd = torch.bfloat16, 64
     assert k.attention_plan(dtype, H, Hkv, hd, page, False)[0] == "prompt_tc5"
     T, cut, far = 731, 500, 37

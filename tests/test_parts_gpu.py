@@ -142,7 +142,7 @@ def test_rmsnorm_part(k, dtype, dim, eps):
     close(got, ref, dtype, "all rows")
     rows = torch.tensor([7, 0, 3], dtype=torch.int32, device="cuda")
     close(norm.forward(ctx, x.cuda(), rows), ref[[7, 0, 3]], dtype, "chosen rows")
-    lazy = norm.forward(ctx, x.cuda(), lazy=True)
+    lazy = norm.pending(ctx, x.cuda())
     assert isinstance(lazy, NormedRows) and torch.equal(lazy.tensor(), got)
 
 
@@ -217,7 +217,7 @@ def test_swiglu_part(k, dtype, D, F, rows):
     ref = P.swiglu(eager.float().cpu().numpy(), tensors["w1"].numpy(), tensors["w3"].numpy(), tensors["w2"].numpy(),
                    np.float64)
     out = torch.zeros((rows, D), device="cuda")
-    ffn.forward(ctx, norm.forward(ctx, x.cuda(), lazy=True), out, False)
+    ffn.forward(ctx, norm.pending(ctx, x.cuda()), out, False)
     close(out, ref, dtype, "pending norm")
 
 
@@ -468,7 +468,7 @@ def test_feed_forward_with_routing_of_the_tests_own(k, dtype, rows):
         ctx = bench.step(slot, [rows])
         x = rnd((rows, D), 131, torch.float32).cuda()
         after_mixer = x.clone()
-        block.mixer.forward(ctx, bench.call, block.mixer_norm.forward(ctx, after_mixer, lazy=True), after_mixer, True)
+        block.mixer.forward(ctx, bench.call, block.mixer_norm.pending(ctx, after_mixer), after_mixer, True)
         xn2 = block.ffn_norm.forward(ctx, after_mixer).float().cpu().numpy().astype(np.float64)
         ref2, _ = plain(xn2)
         bench.call.state.zero_()                  # the same step again through the block, from an empty state

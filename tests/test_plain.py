@@ -142,3 +142,18 @@ def test_sampling_reference_functions():
     p = P.filtered_probs(l, temp=1.0, min_p=0.2)
     assert set(np.nonzero(p)[0]) == {1, 2, 3}                    # exp(-1) = 0.37 stays, exp(-2) = 0.14 goes
     assert np.allclose(P.repeat_penalty(np.array([2.0, -2.0, 1.0]), [0, 1, 0], 2.0), [1.0, -4.0, 1.0])
+
+
+@pytest.mark.parametrize("name,low,high", [("tiny_b", 5e-4, 4e-3), ("loud_a", 1e-2, 3e-2), ("loud_b", 1e-2, 3e-2),
+                                           ("loud_d", 8e-3, 3e-2)])
+def test_error_floor_of_a_bfloat16_pipeline(model_folders, name, low, high):
+    """What bfloat16 costs when nothing else is inexact: float64 arithmetic with only the inputs
+    and outputs of the contractions, the cache and the probabilities rounded.  On the configurations
+    as specified the floor is a tenth of the tolerance; on the loud ones it is above the 2e-2 that
+    holds there, which is why they have a tolerance of their own (helpers.TOL_LOUD)."""
+    exact = P.PlainLfm2(model_folders[name], dtype=np.float64)
+    rounded = P.PlainLfm2(model_folders[name], dtype=np.float64, round_activations=P.to_bf16)
+    toks = helpers.random_tokens(1004, 64, exact.cfg["vocab_size"])
+    floor = helpers.rel_err(rounded.logits(toks), exact.logits(toks))
+    assert low <= floor <= high, floor
+    assert floor < helpers.tol(name, "bfloat16")

@@ -15,9 +15,13 @@ LENGTHS = {"tiny_a": [5, 11, 17, 40, 70], "tiny_b": [1, 2, 9, 33, 64, 100], "tin
 DECODE_TAIL = 32
 
 
+def _lengths(name):
+    return LENGTHS[name.replace("loud_", "tiny_")]
+
+
 def _requests(name):
     vocab = helpers.TINY[name]["config"]["vocab_size"]
-    return {f"r{i}": helpers.random_tokens(1000 + i, n, vocab) for i, n in enumerate(LENGTHS[name])}
+    return {f"r{i}": helpers.random_tokens(1000 + i, n, vocab) for i, n in enumerate(_lengths(name))}
 
 
 def _batches(reqs):
@@ -91,12 +95,12 @@ def test_replay_all_cuts(model_folders, tmp_path, name, dtype):
     plain = PlainLfm2(folder, dtype=np.float64)
     ref = {rid: plain.logits(toks) for rid, toks in reqs.items()}
     steps, expect = build_steps(reqs)
-    live_max = 3 * 64 * (-(-max(LENGTHS[name]) // 64))
+    live_max = 3 * 64 * (-(-max(_lengths(name)) // 64))
     got = helpers.run_trace(folder, dtype, steps, max_tokens=live_max, out_dir=tmp_path / "out")
     worst, where = 0.0, None
     for step, row, rid, pos in expect:
         e = np.max(np.abs(got[step][row].astype(np.float64) - ref[rid][pos])) / np.max(np.abs(ref[rid]))
         if e > worst:
             worst, where = e, (step, row, rid, pos, steps[step]["entries"][0]["id"])
-    print(f"replay {name} {dtype}: worst error {worst:.3e} of max |logit| (tolerance {helpers.TOL[dtype]:.0e})")
-    assert worst <= helpers.TOL[dtype], f"{name} {dtype}: worst error {worst:.3e} at (step,row,req,pos,first id) {where}"
+    print(f"replay {name} {dtype}: worst error {worst:.3e} of max |logit| (tolerance {helpers.tol(name, dtype):.0e})")
+    assert worst <= helpers.tol(name, dtype), f"{name} {dtype}: worst error {worst:.3e} at (step,row,req,pos,first id) {where}"

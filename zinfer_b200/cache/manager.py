@@ -8,9 +8,10 @@ layers only, and `conv_state [n_conv][K-1][D]` zeroed at reset (src/model.zig:14
 * a *slot* is one sequence of a batch: its length, its pages in every group, its row in every
   state tensor.  Slots are handed out by `alloc_slots` and given back by `free_slots`; a freed
   slot's pages return to their pools and are reused by later batches.
-* layers whose mixers ask for the same kind of growing cache (same KV heads, head size and
-  window) form a *group* with storage of its own: K and V tensors
-  [layers of the group, pages, kv heads, page_size, head_dim] and one page table
+* layers whose mixers ask for the same kind of growing cache (same KV heads, widths and
+  window) form a *group* with storage of its own: two tensors
+  [layers of the group, pages, kv heads, page_size, width] (keys and values for attention; a
+  mixer may ask for another width of the second, or for one tensor only) and one page table
   [slots, pages per sequence] shared by the group's layers.  A group with a window gives pages
   back as soon as every position in them has left the window.
 * a mixer that asks for fixed-size state gets a row per slot in a tensor
@@ -61,11 +62,12 @@ class CallCacheSpec:
 
 @dataclass
 class KVView:
-    """One call's keys and values: k, v [pages, kv heads, page_size, head_dim] and the group's
-    page table [slots, pages per sequence] (int32, -1 = no page)."""
+    """One call's growing cache: k [pages, kv heads, page_size, head_dim], v [pages, kv heads,
+    page_size, value_dim] (None if the mixer asked for one tensor only) and the group's page table
+    [slots, pages per sequence] (int32, -1 = no page)."""
 
     k: torch.Tensor
-    v: torch.Tensor
+    v: Optional[torch.Tensor]
     page_table: torch.Tensor
     page_size: int
     window: int
@@ -76,9 +78,10 @@ class KVGroup:
     def __init__(self, request: KVRequest, n_layers: int, num_pages: int, page_size: int, max_slots: int,
                  max_pages_per_seq: int, dtype: torch.dtype, device):
         self.request, self.n_layers, self.num_pages, self.page_size = request, n_layers, num_pages, page_size
-        shape = (n_layers, num_pages, request.n_kv_heads, page_size, request.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (n_layers, num_pages, request.n_kv_heads, page_size)
+        self.k = torch.zeros((*shape, request.head_dim), dtype=dtype, device=device)
+        # the second tensor has the width the mixer asked for, or is absent (one vector per token)
+        self.v = torch.zeros((*shape, request.v_dim), dtype=dtype, device=device) if request.v_dim > 0 else None
         self.table_host = np.full((max_slots, max_pages_per_seq), -1, dtype=np.int32)
         self.table_dev = torch.full((max_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
         self.free_pages = list(range(num_pages - 1, -1, -1))      # pop() hands out page 0 first
@@ -188,7 +191,8 @@ class CacheManager:
             return None
         g, i = self._kv_place[self._kv_of_call[call]]
         grp = self.groups[g]
-        return KVView(grp.k[i], grp.v[i], grp.table_dev, self.page_size, grp.request.window, g)
+        return KVView(grp.k[i], None if grp.v is None else grp.v[i], grp.table_dev, self.page_size,
+                      grp.request.window, g)
 
     def writes_kv(self, call: int) -> bool:
         return self._kv_of_call.get(call) == call

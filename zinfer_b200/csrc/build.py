@@ -1,8 +1,9 @@
 """Compiles the CUDA sources of this folder for sm_100a and loads them through ctypes.
 
 Each `.cu` file becomes one shared library `_build/<name>-<hash>.so`, built by nvcc the first
-time something needs it and reused afterwards; the hash covers every source and header of the
-folder and the flags, so an edit rebuilds what may depend on it.  Nothing here falls back to another
+time something needs it and reused afterwards; the hash covers the source, every file of this
+folder that it includes (directly or through another) and the flags, so an edit rebuilds exactly
+what depends on it.  Nothing here falls back to another
 implementation: a missing compiler or a failed build raises `KernelBuildError`.
 """
 from __future__ import annotations
@@ -10,6 +11,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -67,11 +69,26 @@ def _build_dir() -> Path:
     return d
 
 
+_INCLUDE = re.compile(rb'^[ \t]*#[ \t]*include[ \t]*"([^"]+)"', re.M)
+
+
+def _closure(name: str) -> list[Path]:
+    """`<name>.cu` and the files of this folder it includes, transitively, in a fixed order."""
+    seen: dict[str, Path] = {}
+    todo = [SRC_DIR / f"{name}.cu"]
+    while todo:
+        p = todo.pop()
+        if p.name in seen or not p.is_file():
+            continue
+        seen[p.name] = p
+        todo += [SRC_DIR / m.decode() for m in _INCLUDE.findall(p.read_bytes())]
+    return [seen[k] for k in sorted(seen)]
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
-    # every source and header of the folder: a library may include any of them
-    for p in sorted([*SRC_DIR.glob("*.cu"), *SRC_DIR.glob("*.cuh"), *SRC_DIR.glob("*.h")]):
+    for p in _closure(name):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     return h.hexdigest()[:16]

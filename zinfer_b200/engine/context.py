@@ -49,16 +49,6 @@ def pack_batch(slots: Sequence[int], starts: Sequence[int], token_lists: Sequenc
     return buf
 
 
-def attn_tiles_host(q_lens: Sequence[int], bq: int) -> np.ndarray:
-    """Query tiles of `bq` tokens: rows [tile_seq; tile_q0] as one int32 array [2, n_tiles]."""
-    seq, q0 = [], []
-    for b, l in enumerate(q_lens):
-        for s in range(0, l, bq):
-            seq.append(b)
-            q0.append(s)
-    return np.asarray([seq, q0], dtype=np.int32).reshape(2, len(seq))
-
-
 @dataclass
 class CallContext:
     """What a mixer sees of the schedule entry it runs in."""
@@ -71,54 +61,35 @@ class CallContext:
 
 
 class StepContext:
-    """One step's batch on the device.  Built by the engine; parts only read it."""
+    """One step's batch on the device.  Built by the engine; parts only read it.
+
+    n_tokens, n_seqs; q_lens (host list: tokens each sequence brings), max_q_len, max_kv_len
+    (longest sequence after the step), is_decode (one token for every sequence); the device
+    arrays tokens, tok_seq, tok_pos [n_tokens], cu_q [n_seqs + 1], seq_start, seq_slot [n_seqs];
+    `status` (the device's status word) and `sm_count`.  `memo` keeps what parts derive from the
+    batch's shape alone (tile tables and the like), so that equal parts derive it once a step; a
+    step that is recorded and replayed keeps its memo with the recording."""
 
     def __init__(self, dtype: torch.dtype, device, status: torch.Tensor, buf: torch.Tensor, n_tokens: int,
-                 n_seqs: int, q_lens: Sequence[int], max_kv_len: int, split_keys: int = 0,
-                 tiles: Optional[dict] = None):
+                 n_seqs: int, q_lens: Sequence[int], max_kv_len: int, memo: Optional[dict] = None,
+                 sm_count: int = 0):
         self.dtype, self.device, self.status = dtype, device, status
         self.n_tokens, self.n_seqs = n_tokens, n_seqs
         self.q_lens = list(q_lens)
         self.max_q_len = max(self.q_lens) if self.q_lens else 0
         self.max_kv_len = max_kv_len
         self.is_decode = self.max_q_len == 1 and n_tokens == n_seqs
-        self._split_keys = split_keys
+        self.sm_count = sm_count
         self._buf = buf
         lay = batch_layout(n_tokens, n_seqs)
         for name in ("tokens", "tok_seq", "tok_pos", "cu_q", "seq_start", "seq_slot"):
             o, size = lay[name]
             setattr(self, name, buf[o:o + size])
-        # query-tile tables by tile size; a caller that reuses the same batch shape may share them
-        self._tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = {} if tiles is None else tiles
+        self._memo: dict = {} if memo is None else memo
 
-    def attn_tiles(self, bq: int):
-        """(tile_seq, tile_q0) device arrays for query tiles of `bq` tokens."""
-        t = self._tiles.get(bq)
-        if t is None:
-            host = attn_tiles_host(self.q_lens, bq)
-            dev = torch.from_numpy(host).to(self.device, non_blocking=True)
-            t = (dev[0].contiguous(), dev[1].contiguous())
-            self._tiles[bq] = t
-        return t
-
-    def set_tiles(self, bq: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor) -> None:
-        self._tiles[bq] = (tile_seq, tile_q0)
-
-    def kv_splits(self, n_kv_heads: int) -> tuple[int, int]:
-        """(number of key chunks, keys per chunk) for the attention of this step.  Single-token
-        steps cut the keys so that the GPU's 148 SMs have work (the reference splits single-token
-        attention into up to 16 chunks for its threads, src/model.zig:1941-1955); the cuts lie at
-        multiples of `split_keys`, independent of the batch."""
-        if not self.is_decode or self.max_kv_len <= 0:
-            return 1, 0
-        keys = self._split_keys
-        if keys <= 0:
-            # about four blocks per SM, chunks of 128 to 4096 keys: with unequal sequences a longer
-            # chunk leaves the SMs that drew a short sequence idle (64 sequences of 1K to 32K tokens:
-            # 3.90 ms a step with chunks of 16K keys, 3.27 ms with 4K)
-            blocks = max(1, self.n_seqs * n_kv_heads)
-            want = max(1, -(-592 // blocks))
-            keys = min(4096, max(128, -(-self.max_kv_len // want)))
-            keys = -(-keys // 64) * 64
-        n = -(-self.max_kv_len // keys)
-        return (n, keys) if n > 1 else (1, 0)
+    def memo(self, key, make):
+        """`make()` once per step (or recording) and key."""
+        v = self._memo.get(key)
+        if v is None:
+            v = self._memo[key] = make()
+        return v

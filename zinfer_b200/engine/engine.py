@@ -10,6 +10,7 @@ sequences of unequal length are packed, not padded.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Optional, Sequence
 
 import numpy as np
@@ -19,7 +20,6 @@ from .. import kernels
 from ..cache.manager import CacheManager
 from ..models.model import Model
 from .context import CallContext, StepContext, batch_layout, pack_batch
-from .fused_decode import build as build_fused_plan
 
 
 class StepError(RuntimeError):
@@ -35,30 +35,29 @@ _STATUS_TEXT = {1: "a token id lies outside the vocabulary", 2: "a token's posit
                 15: "the tcgen05 prompt attention gave up waiting for its query or K/V tiles",
                 16: "the tcgen05 prompt attention gave up waiting for the probabilities",
                 17: "the tcgen05 prompt attention gave up waiting for the scores",
-                18: "the tcgen05 prompt attention gave up waiting for P V",
-                21: "the one-kernel single-token step gave up waiting at a grid barrier",
-                22: "the one-kernel single-token step was given an operation it does not take"}
+                18: "the tcgen05 prompt attention gave up waiting for P V"}
 
 
-class _DecodeGraph:
-    """A captured single-token step for one batch size: static input buffer, static output.
+class _DecodeBatch:
+    """What the recorded single-token steps of one batch size share: the static buffer that holds
+    the batch's description, the static logits they write, and what the parts memoised about a
+    batch of this shape.
 
-    The batch's description reaches the static device buffer through a small ring of pinned
-    host buffers: a buffer is rewritten only after the copy that last read it has run, so a host
+    The description reaches the static device buffer through a small ring of pinned host
+    buffers: a buffer is rewritten only after the copy that last read it has run, so a host
     that runs several steps ahead of the device cannot change a step's input under it."""
 
     RING = 4
 
-    def __init__(self, words, device):
+    def __init__(self, n_seqs: int, vocab: int, device):
+        words = batch_layout(n_seqs, n_seqs)["_total"][0]
         self.meta_dev = torch.zeros(words, dtype=torch.int32, device=device)
+        self.logits = torch.empty((n_seqs, vocab), dtype=torch.float32, device=device)
         self._hosts = [torch.zeros(words, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self._copied = [None] * self.RING
         self._next = 0
-        self.tiles: dict = {}
-        self.plan = None            # engine.fused_decode.FusedDecodePlan, or False if the model cannot be fused
-        self.warmed = False
-        self.graph = None
-        self.logits = None
+        self.memo: dict = {}
+        self.warmed = False         # one step of this batch size has run outside a recording (it loads the kernels)
 
     def upload(self, words, dev_tokens: Optional[torch.Tensor] = None) -> None:
         """Copies the packed batch description to the static device buffer; `dev_tokens`, if
@@ -90,23 +89,18 @@ class _PendingTokens:
 
 
 class Engine:
+    MAX_GRAPHS = 48         # recorded single-token steps kept; the least recently used one goes first
+
     def __init__(self, model: Model, max_batch: int = 64, max_seq_len: Optional[int] = None,
                  max_tokens: Optional[int] = None, page_size: int = 64, max_step_tokens: int = 8192,
-                 attn_split_keys: int = 0, use_graphs: bool = True, fused_decode: bool = False,
-                 fused_decode_max_context: int = 4096, lookahead: bool = True):
+                 use_graphs: bool = True, lookahead: bool = True):
         """max_batch: slots (sequences alive at once).  max_seq_len: longest sequence, default
         the model's max_position_embeddings.  max_tokens: tokens the cache holds in total, each
         sequence rounded up to whole pages; default max_batch * max_seq_len.  max_step_tokens:
-        a step with more tokens runs as several packed chunks.  attn_split_keys: keys per
-        chunk of single-token attention (0 = chosen per step).  use_graphs: replay single-token
-        steps of `decode` from CUDA graphs.  fused_decode: run single-token steps of few sequences
-        as one persistent kernel where the model's parts allow it (engine/fused_decode.py), while
-        no sequence is longer than fused_decode_max_context (that kernel does not split a
-        sequence's keys over blocks).  Off by default: measured on a B200 it is slower than the
-        graph of separate kernels (its per-operation barrier and input staging cost what a kernel
-        boundary costs, and its contraction loop issues more instructions per byte).  lookahead:
-        `generate` launches a step before the host has read the previous step's tokens whenever
-        the sampler allows it."""
+        a step with more tokens runs as several packed chunks.  use_graphs: replay single-token
+        steps of `decode` from CUDA graphs (only if every mixer of the model is `capture_safe`).
+        lookahead: `generate` launches a step before the host has read the previous step's tokens
+        whenever the sampler allows it."""
         kernels.require_cuda()
         if model.device is None:
             raise ValueError("the model has no weights loaded")
@@ -117,21 +111,23 @@ class Engine:
         if max_tokens is None:
             max_tokens = max_batch * (-(-self.max_seq_len // page_size) * page_size)
         self.max_step_tokens = max(1, int(max_step_tokens))
-        self.attn_split_keys = int(attn_split_keys)
+        mixers = [layer.mixer for layer in model.layers]
+        for m in mixers:
+            m.check(self.dtype, page_size)       # sizes no kernel takes are refused here, not in the first step
         self.cache = CacheManager(model.cache_specs(), max_batch, int(max_tokens), self.max_seq_len, page_size,
                                   self.dtype, self.device)
         self.calls = [CallContext(c, call.layer, self.cache.kv_view(c), self.cache.writes_kv(c),
                                   self.cache.state_view(c)) for c, call in enumerate(model.schedule)]
         self.status = kernels.status_word(self.device)      # one status word per device, shared by all kernels
+        self.sm_count = kernels.sm_count(self.device)
         self.vocab_size = cfg.vocab_size
-        self.use_graphs = bool(use_graphs)
+        self.use_graphs = bool(use_graphs) and all(getattr(m, "capture_safe", False) for m in mixers)
         self.supports_device_tokens = bool(lookahead)    # GenerationLoop asks this before running ahead
-        self.fused_decode = bool(fused_decode) and self.use_graphs
-        self.fused_decode_max_context = int(fused_decode_max_context)
-        self._fused: dict[int, _DecodeGraph] = {}
-        self.last_fused_ctx = None      # batch of the last fused step (FusedDecodePlan.trace takes it)
-        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._key_mixers = list({id(m): m for m in mixers}.values())
+        self._decode_batches: dict[int, _DecodeBatch] = {}
+        self._graphs: "OrderedDict[tuple, torch.cuda.CUDAGraph]" = OrderedDict()
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
+        self.graph_captures = 0         # steps that were recorded instead of replayed, since the engine was built
         self.stats = None
 
     # ------------------------------------------------------------------ sequences
@@ -223,7 +219,7 @@ class Engine:
         host = pack_batch(slots, starts, token_lists)
         buf = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
         max_kv = max(s + l for s, l in zip(starts, lens))
-        ctx = StepContext(self.dtype, self.device, self.status, buf, n, B, lens, max_kv, self.attn_split_keys)
+        ctx = StepContext(self.dtype, self.device, self.status, buf, n, B, lens, max_kv, sm_count=self.sm_count)
         cu = np.concatenate([[0], np.cumsum(lens)])
         rows = [int(cu[b]) + int(i) for b, w in enumerate(want) for i in w]
         want_rows = torch.tensor(rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True) if rows else None
@@ -235,12 +231,14 @@ class Engine:
         """One token for each sequence, logits [len(slots), vocab] for all of them.  The same
         computation as `step(slots, [[t] for t in tokens])`, replayed from a CUDA graph: a step of
         single tokens is some hundred small kernels, and launching them one by one costs more than
-        running them.  One graph per (batch size, key-chunk layout); its first use runs
-        eagerly (which also loads every kernel), its second use is captured.  With
-        `fused_decode` the step is one launch of the persistent kernel instead.  The returned
-        tensor is a static output buffer: use it before the next call.  `tokens` is a sequence of
-        ints, or an int32 tensor [len(slots)] on the device (a sampler's output): the step then
-        starts without the host having seen them."""
+        running them.  A recording serves a batch size and whatever else the mixers bake into
+        their launches (`Mixer.launch_key`: for attention the layout of key chunks, which changes
+        when the longest sequence outgrows 512, 768, 1024, 1536, ... tokens).  The first step of a
+        batch size runs unrecorded (which also loads every kernel); later ones are recorded at
+        their first use and replayed from then on.  The returned tensor is a static buffer of
+        the batch size: use it before the next call.  `tokens` is a sequence of ints, or an int32
+        tensor [len(slots)] on the device (a sampler's output): the step then starts without the
+        host having seen them."""
         on_device = isinstance(tokens, torch.Tensor)
         if not self.use_graphs:
             host = tokens.cpu().tolist() if on_device else tokens
@@ -258,43 +256,77 @@ class Engine:
         self.cache.sync()
         starts = [int(self.cache.lengths[s]) for s in slots]
         words = pack_batch(slots, starts, [[int(t)] for t in tokens])
-        logits = None
-        if self.fused_decode and max(starts) + 1 <= self.fused_decode_max_context:
-            entry = self._fused.get(B)
-            if entry is None:
-                entry = self._fused[B] = _DecodeGraph(batch_layout(B, B)["_total"][0], self.device)
-                entry.plan = build_fused_plan(self, B) or False
-            if entry.plan:
-                entry.upload(words, dev_tokens)
-                ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max(starts) + 1)
-                logits = entry.plan.run(ctx)
-                self.last_fused_ctx = ctx
-        if logits is None:
-            logits = self._decode_graph(B, words, ones, max(starts) + 1, dev_tokens)
+        batch = self._decode_batch(B)
+        batch.upload(words, dev_tokens)
+        logits = self._decode_graph(batch, B, max(starts) + 1)
         self.cache.advance(slots, ones)
         if check:
             self.check_status()
         return logits
 
-    def _decode_graph(self, B, words, ones, longest, dev_tokens=None) -> torch.Tensor:
-        max_kv = -(-longest // 512) * 512            # bucketed, so that the key changes rarely
-        key = (B, max_kv)
-        entry = self._graphs.get(key)
-        if entry is None:
-            entry = self._graphs[key] = _DecodeGraph(batch_layout(B, B)["_total"][0], self.device)
-        entry.upload(words, dev_tokens)
-        ctx = StepContext(self.dtype, self.device, self.status, entry.meta_dev, B, B, ones, max_kv,
-                          self.attn_split_keys, tiles=entry.tiles)
-        if entry.graph is None and not entry.warmed:
-            entry.warmed = True
-            return self.model.forward(ctx, self.calls, None, want_all=True)
-        if entry.graph is None:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, pool=self._graph_pool):
-                entry.logits = self.model.forward(ctx, self.calls, None, want_all=True)
-            entry.graph = g
-        entry.graph.replay()
-        return entry.logits
+    def _decode_batch(self, B: int) -> _DecodeBatch:
+        batch = self._decode_batches.get(B)
+        if batch is None:
+            batch = self._decode_batches[B] = _DecodeBatch(B, self.vocab_size, self.device)
+        return batch
+
+    def decode_key(self, n_seqs: int, longest: int) -> tuple:
+        """What a recorded single-token step is good for: the batch size and every mixer's launch key."""
+        return (n_seqs, *(m.launch_key(n_seqs, longest) for m in self._key_mixers))
+
+    def _decode_graph(self, batch: _DecodeBatch, B: int, longest: int) -> torch.Tensor:
+        ctx = StepContext(self.dtype, self.device, self.status, batch.meta_dev, B, B, [1] * B, longest,
+                          memo=batch.memo, sm_count=self.sm_count)
+        if not batch.warmed:
+            batch.warmed = True
+            self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+            return batch.logits
+        key = self.decode_key(B, longest)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+            self._graphs[key] = graph
+            self.graph_captures += 1
+            while len(self._graphs) > self.MAX_GRAPHS:
+                self._graphs.popitem(last=False)
+        else:
+            self._graphs.move_to_end(key)
+        graph.replay()
+        return batch.logits
+
+    def prepare_decode(self, n_seqs: int, first: int, last: int) -> None:
+        """Records, ahead of time, the single-token steps that `n_seqs` sequences need while their
+        longest grows from `first` to `last` tokens (one per launch key on the way), so that none of
+        those steps pays for a recording.  Needs one unrecorded step of that batch size to have run."""
+        if not self.use_graphs:
+            return
+        batch = self._decode_batch(n_seqs)
+        if not batch.warmed:
+            raise RuntimeError(f"no single-token step of {n_seqs} sequences has run yet")
+        longest = max(first, last)
+        length = max(1, first)
+        while True:
+            key = self.decode_key(n_seqs, length)
+            if key not in self._graphs:
+                ctx = StepContext(self.dtype, self.device, self.status, batch.meta_dev, n_seqs, n_seqs, [1] * n_seqs,
+                                  length, memo=batch.memo, sm_count=self.sm_count)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+                self._graphs[key] = graph
+                self.graph_captures += 1
+            if length >= longest:
+                break
+            # the next length at which some mixer's key may change: keys are functions of coarse
+            # buckets, so doubling steps with a linear probe in between find every one of them
+            nxt = length + 1
+            while nxt < longest and self.decode_key(n_seqs, nxt) == key:
+                nxt = min(longest, nxt + max(1, nxt // 8))
+            length = nxt
+        while len(self._graphs) > self.MAX_GRAPHS:
+            self._graphs.popitem(last=False)
 
     # ------------------------------------------------------------------ generation
     def prefill(self, slots, prompts) -> torch.Tensor:

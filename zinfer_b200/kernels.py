@@ -69,13 +69,6 @@ _SIGNATURES = {
         "zk_attn_decode_tc": "pppppppppiiiiiiifiip",
         "zk_attn_decode_tc_takes": "iiii",
     },
-    "fused_decode": {
-        "zk_fused_decode": "piippppp" + "ipp",
-        "zk_fused_decode_op_bytes": "",
-        "zk_fused_decode_max_rows": "",
-        "zk_fused_decode_max_staged_k": "i",
-        "zk_fused_decode_attn_takes": "iiii",
-    },
     "sampling": {
         "zk_apply_penalties": "piipifppip",
         "zk_argmax": "piipp",
@@ -125,6 +118,8 @@ def _error_name(code: int) -> str:
 # Number of kernel launches made through this module since import (the benchmark reports it).
 launch_count = 0
 
+_device_state: dict = {}
+
 
 def _check(code: int, what: str) -> None:
     global launch_count
@@ -137,6 +132,16 @@ def require_cuda() -> None:
     """Raises unless a CUDA device is usable; the product path has no CPU implementation."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: zinfer_b200 runs on sm_100a GPUs only and has no CPU path")
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device; launch plans size their grids by it."""
+    dev = torch.device("cuda" if device is None else device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    n = _device_state.setdefault(("sm_count", idx), None)
+    if n is None:
+        n = _device_state[("sm_count", idx)] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
 
 
 def _stream() -> int:
@@ -242,9 +247,6 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
                                             out.stride(0), dtype_code(a.dtype), dtype_code(out.dtype),
                                             1 if accumulate else 0, _stream()), "gemm_simt")
     return out
-
-
-_device_state: dict = {}
 
 
 def status_word(device) -> torch.Tensor:
@@ -644,54 +646,6 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
                                                  num_splits, dtype_code(q.dtype), _stream()), "attention merge")
     return out
-
-
-# ------------------------------------------------------------------------------- fused single-token step
-
-class FusedOp(ctypes.Structure):
-    """One operation of the fused single-token step; mirrors `struct Op` of csrc/fused_decode.cu."""
-
-    _fields_ = ([(n, ctypes.c_int) for n in ("kind", "xin", "epi", "rg", "N", "K", "ldw", "ldx", "ldc", "taps", "H", "Hkv",
-                                             "hd", "n_rot", "rope_interleaved", "page_size", "window", "pt_stride",
-                                             "vocab", "pad0")]
-                + [("eps", ctypes.c_float), ("scale", ctypes.c_float), ("state_stride", ctypes.c_longlong)]
-                + [(n, ctypes.c_void_p) for n in ("W", "X", "norm_w", "C", "bias", "conv_state", "conv_taps", "conv_bias",
-                                                  "k_cache", "v_cache", "q_norm", "k_norm", "inv_freq", "page_table",
-                                                  "table")])
-
-
-FUSED_OP_EMBED, FUSED_OP_GEMM, FUSED_OP_ATTN = 0, 1, 2
-FUSED_XIN_BF16, FUSED_XIN_NORM = 0, 1
-FUSED_EPI_BF16, FUSED_EPI_ACC_F32, FUSED_EPI_F32, FUSED_EPI_SWIGLU, FUSED_EPI_CONV = 0, 1, 2, 3, 4
-
-
-def fused_decode_limits(n_rows: int = 1) -> dict:
-    """Sizes the fused single-token kernel takes: most rows, and the longest row it can normalise
-    in a step of `n_rows` sequences."""
-    if ctypes.sizeof(FusedOp) != _fn("fused_decode", "zk_fused_decode_op_bytes")():
-        raise KernelError("fused_decode: the Python and CUDA layouts of an operation differ")
-    return {"max_rows": _fn("fused_decode", "zk_fused_decode_max_rows")(),
-            "max_staged_k": _fn("fused_decode", "zk_fused_decode_max_staged_k")(n_rows)}
-
-
-def fused_decode_attn_takes(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
-    return bool(_fn("fused_decode", "zk_fused_decode_attn_takes")(n_heads, n_kv, head_dim, page_size))
-
-
-def fused_decode(ops: torch.Tensor, n_ops: int, n_rows: int, tokens, seq_start, seq_slot, barrier, status,
-                 n_blocks: int, trace: Optional[torch.Tensor] = None) -> None:
-    """Runs the program in `ops` (uint8 tensor of `n_ops` FusedOp records) for `n_rows` sequences;
-    `barrier` holds an int32 word that is zero at launch."""
-    _need(ops, "ops", torch.uint8)
-    _need(barrier, "barrier", torch.int32)
-    if trace is not None:
-        _need(trace, "trace", torch.int64)
-        if trace.numel() < 4 * n_ops:
-            raise KernelError("fused_decode: the trace buffer holds fewer than 4 stamps per operation")
-    _check(_fn("fused_decode", "zk_fused_decode")(_ptr(ops), n_ops, n_rows, _ptr(tokens), _ptr(seq_start),
-                                                  _ptr(seq_slot), _ptr(barrier), _ptr(status), n_blocks,
-                                                  _ptr(trace) if trace is not None else None, _stream()),
-           "fused_decode")
 
 
 # ------------------------------------------------------------------------------- sampling

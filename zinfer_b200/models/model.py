@@ -12,6 +12,7 @@ import torch
 from ..cache.manager import CallCacheSpec
 from ..config.base import ModelConfig
 from ..parts.base import Block, Norm, Part, WeightSpec, walk_parts
+from ..parts.block import normed_for
 from ..parts.embedding import LMHead, TokenEmbedding
 
 
@@ -75,16 +76,17 @@ class Model:
         return specs
 
     # ------------------------------------------------------------------ forward
-    def forward(self, ctx, calls, want_rows: Optional[torch.Tensor], want_all: bool = False) -> Optional[torch.Tensor]:
+    def forward(self, ctx, calls, want_rows: Optional[torch.Tensor], want_all: bool = False,
+                out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the step's tokens through every schedule entry; returns float32 logits of the rows
-        listed in `want_rows` (row indices into the packed tokens), of every row with `want_all`,
-        or None when none is wanted.  Only wanted rows meet the final norm and the head
-        (src/model.zig:2482-2490)."""
+        listed in `want_rows` (row indices into the packed tokens), of every row with `want_all`
+        (written into `out` if given), or None when none is wanted.  Only wanted rows meet the
+        final norm and the head (src/model.zig:2482-2490)."""
         x = self.embedding.forward(ctx, ctx.tokens)
         for call_ctx in calls:
             self.layers[call_ctx.layer].forward(ctx, call_ctx, x)
         if want_all:
-            return self.head.forward(ctx, self.final_norm.forward(ctx, x, lazy=True))
+            return self.head.forward(ctx, normed_for(self.head, self.final_norm, ctx, x), out=out)
         if want_rows is None or want_rows.numel() == 0:
             return None
         xn = self.final_norm.forward(ctx, x, rows=want_rows)

@@ -9,12 +9,18 @@ written to the cache at the tokens' absolute positions; every query then attends
 (src/model.zig:1988-1990).  Scores are scaled by 1/sqrt(head_dim) (src/model.zig:465).
 
 A call that reads another call's cache (`call.writes_kv` False) computes only its queries.
+
+How the kernels are launched is decided here, not by the engine: the table of query tiles of a
+step, and for single-token steps the cut of a sequence's keys into chunks that separate blocks
+walk (the reference cuts single-token attention into up to 16 chunks for its threads,
+src/model.zig:1941-1955).
 """
 from __future__ import annotations
 
 import math
-from typing import Optional
+from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -22,13 +28,64 @@ from .base import MIXERS, KVRequest, Mixer, PositionEncoding, WeightSpec
 from .linear import linear
 
 
+def query_tiles(q_lens: Sequence[int], bq: int) -> np.ndarray:
+    """Query tiles of `bq` tokens: rows [tile_seq; tile_q0] as one int32 array [2, n_tiles]."""
+    seq, q0 = [], []
+    for b, l in enumerate(q_lens):
+        for s in range(0, l, bq):
+            seq.append(b)
+            q0.append(s)
+    return np.asarray([seq, q0], dtype=np.int32).reshape(2, len(seq))
+
+
+def key_capacity(longest: int) -> int:
+    """The smallest of 512, 768, 1024, 1536, 2048, 3072, ... that holds `longest` keys.  The chunks of a
+    single-token step are laid out for this capacity, not for the longest sequence itself, so
+    that the layout (which a recorded step bakes in) changes a few times in a sequence's life
+    instead of every few hundred tokens; chunks beyond a sequence's end cost a block that exits."""
+    cap = 512
+    while cap < longest:
+        cap = cap * 3 // 2 if cap & (cap - 1) == 0 else cap // 3 * 4
+    return cap
+
+
+CHUNK_ALIGN = 64            # chunk boundaries the single-token kernels take (their key tile)
+
+
+def key_chunks(n_seqs: int, n_kv_heads: int, longest: int, sm_count: int, split_keys: int = 0) -> tuple[int, int]:
+    """(number of key chunks, keys per chunk) for single-token attention of `n_seqs` sequences up to
+    `longest` tokens long.  The cuts lie at multiples of the chunk size, whatever the batch, and
+    the chunks are added in order by the merge kernel, so a sequence's result does not depend on its
+    neighbours.  split_keys > 0 fixes the chunk size; otherwise it is chosen so that about four
+    blocks per SM have work, between 128 and 4096 keys: with unequal sequences a longer chunk
+    leaves the SMs that drew a short sequence idle (64 sequences of 1K to 32K tokens on a B200:
+    3.90 ms a step with chunks of 16K keys, 3.27 ms with 4K)."""
+    if longest <= 0:
+        return 1, 0
+    cap = key_capacity(longest)
+    keys = split_keys
+    if keys <= 0:
+        blocks = max(1, n_seqs * n_kv_heads)
+        want = max(1, -(-4 * max(sm_count, 1) // blocks))
+        keys = min(4096, max(128, -(-cap // want)))
+        keys = -(-keys // CHUNK_ALIGN) * CHUNK_ALIGN
+    n = -(-cap // keys)
+    return (n, keys) if n > 1 else (1, 0)
+
+
 class GqaAttention(Mixer):
+    capture_safe = True
+
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, q_name: str, k_name: str,
                  v_name: str, out_name: str, q_norm_name: Optional[str] = None, k_norm_name: Optional[str] = None,
                  norm_eps: float = 1e-5, position: Optional[PositionEncoding] = None, window: int = 0,
-                 scale: Optional[float] = None):
+                 scale: Optional[float] = None, split_keys: int = 0):
+        """split_keys: keys per chunk of single-token attention, a multiple of 64 (0 = chosen per
+        step from the batch and the GPU's size)."""
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} KV heads")    # src/model.zig:487
+        self.split_keys = int(split_keys)
+        self._sm_count = 0
         self.hidden, self.n_heads, self.n_kv, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
         self.q_name, self.k_name, self.v_name, self.out_name = q_name, k_name, v_name, out_name
         self.q_norm_name, self.k_norm_name = q_norm_name, k_norm_name
@@ -62,9 +119,20 @@ class GqaAttention(Mixer):
         self.w_out = weights[self.out_name]
         self.q_norm = weights[self.q_norm_name] if self.q_norm_name else None
         self.k_norm = weights[self.k_norm_name] if self.k_norm_name else None
+        self._sm_count = kernels.sm_count(device) if torch.device(device).type == "cuda" else 0
 
     def kv_request(self):
         return KVRequest(self.n_kv, self.head_dim, self.window)
+
+    def check(self, dtype, page_size):
+        most = kernels.attn_max_head_dim()
+        if self.head_dim % 2 or self.head_dim > most:        # the reference: a multiple of 8, at most 512 (src/model.zig:1469)
+            raise ValueError(f"attention: head_dim {self.head_dim} must be even and at most {most}")
+        if self.split_keys < 0 or self.split_keys % CHUNK_ALIGN:
+            raise ValueError(f"attention: split_keys {self.split_keys} must be a multiple of {CHUNK_ALIGN}")
+
+    def launch_key(self, n_seqs, longest):
+        return key_chunks(n_seqs, self.n_kv, longest, self._sm_count, self.split_keys)
 
     takes_pending_norm = True
 
@@ -89,12 +157,19 @@ class GqaAttention(Mixer):
                                    write_kv=call.writes_kv, **common)
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
                                                    ctx.is_decode, self.window)
-        tile_seq, tile_q0 = ctx.attn_tiles(tile_tokens)
-        num_splits, split_keys = ctx.kv_splits(self.n_kv)
+        tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: self._tiles_on_device(ctx, tile_tokens))
+        num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
+                                  if ctx.is_decode else (1, 0))
         att = kernels.attention(q, kv.k, kv.v, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot,
                                 kv.page_table, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
                                 num_splits, split_keys, single_token=ctx.is_decode, kind=kind)
         linear(att, self.w_out, out=out, accumulate=accumulate)
+
+
+    @staticmethod
+    def _tiles_on_device(ctx, tile_tokens: int):
+        dev = torch.from_numpy(query_tiles(ctx.q_lens, tile_tokens)).to(ctx.device, non_blocking=True)
+        return dev[0].contiguous(), dev[1].contiguous()
 
 
 MIXERS.register("gqa_attention", GqaAttention)

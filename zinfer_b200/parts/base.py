@@ -11,11 +11,16 @@ Interfaces
 ----------
 Part            weight_specs() -> [WeightSpec]; load(weights: dict name -> tensor, dtype, device)
 Norm            forward(ctx, x_f32, rows=None) -> tensor in the run dtype
+                pending(ctx, x_f32) -> object | None   optional: the norm not yet applied, for a
+                                                       consumer that can apply it itself
 PositionEncoding  rotary() -> RotaryParams | None (lets the mixer fuse it), or
                   apply(ctx, q, k) -> None to rotate / shift in place on its own
 Mixer           kv_request() -> KVRequest | None      growing cache it needs
                 state_request() -> StateRequest | None  fixed-size per-sequence state it needs
                 forward(ctx, call, xn, out, accumulate)  out (+)= mixer(xn); out is float32
+                check(dtype, page_size)               refuse sizes no kernel takes, at engine set-up
+                capture_safe                          whether forward may be recorded in a CUDA graph
+                launch_key(n_seqs, longest)           what a recorded single-token step bakes in
 FeedForward     forward(ctx, xn, out, accumulate)
 Block           forward(ctx, call, x)  updates the float32 residual stream x in place
 """
@@ -49,12 +54,20 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class KVRequest:
-    """A growing per-token cache: keys and values of `n_kv_heads` x `head_dim` per token.
+    """A growing per-token cache.  Per token and layer it holds `n_kv_heads` rows of `head_dim`
+    values in a first tensor ("k") and `n_kv_heads` rows of `value_dim` values in a second ("v").
+    value_dim None = as wide as head_dim (keys and values of attention); value_dim 0 = no
+    second tensor (a mixer that keeps one vector per token, e.g. a latent).
     window = 0 keeps every token; window = W lets the cache drop tokens more than W behind."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: Optional[int] = None
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -86,7 +99,14 @@ class Part:
 
 class Norm(Part):
     def forward(self, ctx, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The normalised rows of float32 `x` (all, or those listed in `rows`) in the run dtype."""
         raise NotImplementedError
+
+    def pending(self, ctx, x: torch.Tensor):
+        """The norm of all rows of `x` as an object that a consumer with `takes_pending_norm`
+        resolves itself (parts.linear.NormedRows), or None if this norm has no such form; the
+        caller then uses `forward`."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -98,10 +118,26 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # Whether `forward` may be recorded into a CUDA graph: it launches kernels on the current
+    # stream only, reads nothing back to the host, and its launches depend on the batch only
+    # through (number of sequences, launch_key).  The engine replays single-token steps from
+    # graphs only if every mixer of the model says so; otherwise it runs them one by one.
+    capture_safe = False
+
     def kv_request(self) -> Optional[KVRequest]:
         return None
 
     def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def check(self, dtype: torch.dtype, page_size: int) -> None:
+        """Raises ValueError if no kernel of this mixer takes its sizes with this run dtype and
+        page size.  Called once when an engine is built, before anything runs."""
+
+    def launch_key(self, n_seqs: int, longest: int):
+        """What a recorded single-token step of `n_seqs` sequences, the longest of which then has
+        `longest` tokens, bakes into its launches besides `n_seqs` (any hashable; None = nothing).
+        A recorded step is replayed only for batches that give the same key."""
         return None
 
     def forward(self, ctx, call, xn: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:

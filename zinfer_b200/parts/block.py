@@ -2,8 +2,9 @@
 (src/model.zig:2395-2422).  The residual stream x is float32; each sum is the `accumulate`
 store of the part's last contraction (src/model.zig:918-920).
 
-A part that sets `takes_pending_norm = True` receives its input as a `NormedRows` (the norm not
-yet applied) and passes it to `linear` or a fused kernel; any other part receives a tensor."""
+A part that sets `takes_pending_norm = True` receives its input as the norm's `pending` form (a
+`NormedRows`: the norm not yet applied) when the norm has one, and passes it to `linear` or a
+fused kernel; any other part, and any part behind a norm without that form, receives a tensor."""
 from __future__ import annotations
 
 from .base import BLOCKS, Block, FeedForward, Mixer, Norm
@@ -17,10 +18,17 @@ class PreNormBlock(Block):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
     def forward(self, ctx, call, x):
-        xn = self.mixer_norm.forward(ctx, x, lazy=getattr(self.mixer, "takes_pending_norm", False))
-        self.mixer.forward(ctx, call, xn, x, True)
-        xn = self.ffn_norm.forward(ctx, x, lazy=getattr(self.ffn, "takes_pending_norm", False))
-        self.ffn.forward(ctx, xn, x, True)
+        self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x), x, True)
+        self.ffn.forward(ctx, normed_for(self.ffn, self.ffn_norm, ctx, x), x, True)
+
+
+def normed_for(consumer, norm: Norm, ctx, x):
+    """norm(x) for `consumer`: still pending if the consumer takes that and the norm offers it."""
+    if getattr(consumer, "takes_pending_norm", False):
+        p = norm.pending(ctx, x)
+        if p is not None:
+            return p
+    return norm.forward(ctx, x)
 
 
 BLOCKS.register("prenorm", PreNormBlock)

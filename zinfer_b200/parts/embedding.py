@@ -40,6 +40,9 @@ class LMHead(Part):
     def load(self, weights, dtype, device):
         self.weight = None if self.weight_name is None else weights[self.weight_name]
 
-    def forward(self, ctx, xn: torch.Tensor) -> torch.Tensor:
+    takes_pending_norm = True
+
+    def forward(self, ctx, xn, out: torch.Tensor | None = None) -> torch.Tensor:
+        """float32 logits of the rows of xn (a tensor, or a norm still pending), into `out` if given."""
         w = self.weight if self.weight is not None else self.embedding.weight
-        return linear(xn, w, out_dtype=torch.float32)
+        return linear(xn, w, out=out, out_dtype=torch.float32)

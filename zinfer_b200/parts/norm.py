@@ -22,12 +22,12 @@ class RMSNorm(Norm):
     def load(self, weights, dtype, device):
         self.weight = weights[self.weight_name]
 
-    def forward(self, ctx, x, rows=None, lazy=False):
-        """The normalised rows in the run dtype.  With `lazy` (and all rows wanted) a `NormedRows`
-        is returned instead, which `linear` and the fused kernels resolve."""
-        if lazy and rows is None:
-            return NormedRows(x, self.weight, self.eps, ctx.dtype)
+    def forward(self, ctx, x, rows=None):
         return kernels.rmsnorm(x, self.weight, self.eps, ctx.dtype, rows)
+
+    def pending(self, ctx, x):
+        """All rows, not yet normalised: `linear` and the fused kernels resolve a `NormedRows`."""
+        return NormedRows(x, self.weight, self.eps, ctx.dtype)
 
 
 NORMS.register("rmsnorm", RMSNorm)

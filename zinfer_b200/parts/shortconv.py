@@ -20,6 +20,8 @@ from .linear import FUSION_GROUP, fused_input, interleave_rows, linear
 
 
 class ShortConv(Mixer):
+    capture_safe = True        # kernels on the current stream only; launches depend on the batch size alone
+
     def __init__(self, hidden: int, kernel_size: int, in_name: str, conv_name: str, out_name: str,
                  conv_bias_name: str | None = None, in_bias_name: str | None = None,
                  out_bias_name: str | None = None):

@@ -51,18 +51,51 @@ def random_tensors(model, seed: int, std: float = 0.02, norm_init: str = "one_pl
         yield spec, _tensor(spec, seed, std, norm_init, storage_dtype)
 
 
+def random_tensors_on_device(model, seed: int, std: float, norm_init: str, storage_dtype: torch.dtype,
+                             device) -> Iterator[tuple[WeightSpec, torch.Tensor]]:
+    """As `random_tensors`, drawn by a kernel on the GPU: other values than the host generator's,
+    the same distribution, a function of (seed, tensor name, element index) only; a billion
+    parameters in milliseconds.  Storage is float32 or bfloat16."""
+    from .. import kernels
+
+    if storage_dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"the device fill stores float32 or bfloat16, not {storage_dtype}")
+    for name, spec in model.weight_specs().items():
+        if spec.init == "skip":
+            continue
+        if spec.role == "table":
+            raise ValueError(f"tensor '{name}': integer tables have no random fill")
+        init = norm_init if spec.init == "norm" else spec.init
+        t = torch.empty(spec.alt_shapes[0] if spec.alt_shapes else spec.shape, dtype=storage_dtype, device=device)
+        if init == "zeros":
+            t.zero_()
+        elif init in ("normal", "one_plus_normal"):
+            kernels.fill_normal(t, (seed << 32) ^ zlib.crc32(name.encode()), 1.0 if init == "one_plus_normal" else 0.0, std)
+        else:
+            raise ValueError(f"tensor '{name}': unknown init {spec.init!r}")
+        yield spec, t
+
+
 def write_random_model(folder, config: ModelConfig, seed: int, std: float = 0.02,
-                       norm_init: str = "one_plus_normal", storage_dtype: torch.dtype = torch.bfloat16) -> Path:
-    """Writes config.json and model.safetensors for `config` into `folder` (created if needed)."""
+                       norm_init: str = "one_plus_normal", storage_dtype: torch.dtype = torch.bfloat16,
+                       fill_on_device: bool = False, device="cuda") -> Path:
+    """Writes config.json and model.safetensors for `config` into `folder` (created if needed).
+    `fill_on_device` draws the values with the GPU's fill kernel (see `random_tensors_on_device`),
+    which is what a model of a billion parameters wants."""
     import zinfer_b200.models  # noqa: F401
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     model = build_model(config)
-    tensors = {spec.name: t for spec, t in random_tensors(model, seed, std, norm_init, storage_dtype)}
+    if fill_on_device:
+        tensors = {spec.name: t.cpu() for spec, t in
+                   random_tensors_on_device(model, seed, std, norm_init, storage_dtype, device)}
+    else:
+        tensors = {spec.name: t for spec, t in random_tensors(model, seed, std, norm_init, storage_dtype)}
     (folder / "config.json").write_text(json.dumps(config.to_json_dict(), indent=2) + "\n")
     write_safetensors(folder / "model.safetensors", tensors,
-                      metadata={"format": "pt", "seed": str(seed), "std": str(std), "norm_init": norm_init})
+                      metadata={"format": "pt", "seed": str(seed), "std": str(std), "norm_init": norm_init,
+                                "generator": "device" if fill_on_device else "host"})
     return folder
 
 
@@ -70,29 +103,15 @@ def random_model(config: ModelConfig, seed: int, dtype: torch.dtype = torch.bflo
                  std: float = 0.02, norm_init: str = "one_plus_normal",
                  storage_dtype: torch.dtype = torch.bfloat16, fill_on_device: bool = False):
     """A model with random weights, without touching the disk.  By default the values are those
-    `write_random_model` would store for the same seed.  `fill_on_device` draws them with a kernel
-    on the GPU instead (other values, same distribution): a billion parameters in milliseconds."""
+    `write_random_model` would store for the same seed; `fill_on_device` draws them on the GPU
+    instead (the values `write_random_model(fill_on_device=True)` stores).  Either way they are
+    rounded to `storage_dtype` first, so a bfloat16 and a float32 model of one seed hold the same
+    numbers."""
     import zinfer_b200.models  # noqa: F401
 
     model = build_model(config)
-    weights = {}
-    if fill_on_device:
-        from .. import kernels
-
-        for name, spec in model.weight_specs().items():
-            if spec.init == "skip":
-                continue
-            init = norm_init if spec.init == "norm" else spec.init
-            kept = dtype if spec.role == "matrix" else torch.float32
-            t = torch.empty(spec.shape, dtype=storage_dtype if storage_dtype in (torch.float32, torch.bfloat16) else kept,
-                            device=device)
-            if init == "zeros":
-                t.zero_()
-            else:
-                kernels.fill_normal(t, (seed << 32) ^ zlib.crc32(name.encode()), 1.0 if init == "one_plus_normal" else 0.0, std)
-            weights[name] = t.to(kept)
-    else:
-        for spec, t in random_tensors(model, seed, std, norm_init, storage_dtype):
-            weights[spec.name] = convert(t, spec, dtype).to(device).contiguous()
+    draw = (random_tensors_on_device(model, seed, std, norm_init, storage_dtype, device) if fill_on_device
+            else random_tensors(model, seed, std, norm_init, storage_dtype))
+    weights = {spec.name: convert(t, spec, dtype).to(device).contiguous() for spec, t in draw}
     model.load_weights(weights, dtype, device)
     return model
