@@ -140,3 +140,30 @@ def test_streaming_callback_sees_every_emitted_token():
     seen = []
     res, *_ = run(PROMPTS[:2], SCRIPTS[:2], max_batch=2, max_new_tokens=3, stop_ids=[STOP], on_step=lambda d: seen.append(dict(d)))
     assert seen == [{0: 10, 1: 20}, {0: 11, 1: 21}, {1: 22}]
+
+
+def test_interruption_returns_what_was_generated_so_far():
+    """The flag is polled once per step (src/gen.zig:476-479): running requests end with their
+    tokens and the reason "interrupted", requests of later batches come back empty, every slot is
+    given back, and a request that ended before the flag keeps its own reason."""
+    be = Script(PROMPTS, SCRIPTS, 2)
+    loop = GenerationLoop(be, 2, 10_000, 1000, 16)
+    seen = []
+
+    def on_step(d):
+        seen.append(dict(d))
+        if len(seen) == 2:
+            loop.interrupt.set()
+
+    res = loop.run(PROMPTS, PassThrough(), max_new_tokens=5, stop_ids=[STOP], on_step=on_step)
+    assert sorted(be.free) == [0, 1]
+    assert [r.tokens for r in res] == [[10, 11], [20, 21], [], [], []]
+    assert [r.finish_reason for r in res] == ["interrupted"] * 5
+    assert sum(1 for e in be.log if e[0] == "start") == 1 and sum(1 for e in be.log if e[0] == "decode") == 1
+
+    # a request that stopped before the flag was set keeps "stop"
+    prompts, scripts = [[0, 7], [1, 8]], [[STOP], [30, 31, 32, 33, 34]]
+    be = Script(prompts, scripts, 2)
+    loop = GenerationLoop(be, 2, 10_000, 1000, 16)
+    res = loop.run(prompts, PassThrough(), max_new_tokens=5, stop_ids=[STOP], on_step=lambda d: loop.interrupt.set())
+    assert [(r.tokens, r.finish_reason) for r in res] == [([], "stop"), ([30], "interrupted")]

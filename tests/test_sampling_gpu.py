@@ -71,6 +71,24 @@ def test_ties_are_cut_in_index_order(k):
     assert all(p[g] > 0 for g in got) and got[3] == int(np.nonzero(p)[0].max())
 
 
+def test_top_p_cut_is_the_same_in_every_run(k):
+    """The masses that decide the top-p cut are summed in an order-independent way: the same rows
+    and uniforms give the same tokens run after run, also for rows made so that the cut lies at a
+    bin boundary (many equal values, top-k off)."""
+    V, n = 65536, 64
+    x = logits_rows(n, V, 21)
+    x[: n // 2] = np.round(x[: n // 2] * 4) / 4            # few distinct values: cuts fall between whole groups
+    u = np.random.default_rng(22).random((n, 2)).astype(np.float32)
+    xs, us = torch.from_numpy(x).cuda(), torch.from_numpy(u).cuda()
+    for top_p in (0.3, 0.9):
+        first = k.sample(xs, us, temp=1.0, top_p=top_p).cpu().tolist()
+        for _ in range(8):
+            assert k.sample(xs, us, temp=1.0, top_p=top_p).cpu().tolist() == first
+        for i in (0, n - 1):
+            p = P.filtered_probs(x[i], 1.0, top_p=top_p)
+            assert p[first[i]] > 0
+
+
 def test_distribution_of_many_draws(k):
     V, n = 50, 4000
     row = logits_rows(1, V, 9, 1.5)

@@ -1,11 +1,11 @@
 """The entry point that allocates nothing (csrc/attention_decode_noalloc.h), called through its
-exported C symbol: two calls in a row with different batches must equal the regular, allocating
-entry point; a call too large for the built-in scratch is refused with a message.
+exported C symbol: calls in a row with different batches must equal the regular, allocating
+entry point and a float64 evaluation of the same attention on the host, row by row; the device
+memory in use is the same before and after a call; a call too large for the built-in scratch is
+refused with a message.
 
-Who needs it: a host that cannot call cudaMalloc when attention has to run -- inside a stream
-capture, in a real-time loop that must not take the allocator's lock, or after its memory budget
-has been closed.  This file sorts last on purpose, so that a run that stops at the first failure
-has run every other test before."""
+Who needs it: a host that cannot call cudaMalloc when attention has to run -- in a real-time
+loop that must not take the allocator's lock, or after its memory budget has been closed."""
 import ctypes
 
 import numpy as np
@@ -72,20 +72,50 @@ def regular(c, H, Hkv, hd, window, scale, splits, keys):
                              single_token=True)
 
 
-def test_two_calls_in_a_row_equal_the_allocating_entry_point(lib):
+def exact(c, lens, H, Hkv, hd, page, window, scale):
+    """The same attention in float64 on the host: row b of the result is sequence b's [H * hd]."""
+    q, k, v = c["q"].double().cpu(), c["k"].double().cpu(), c["v"].double().cpu()
+    table, slots = c["table"].cpu(), c["seq_slot"].cpu().tolist()
+    out = torch.zeros(len(lens), H * hd, dtype=torch.float64)
+    for b, L in enumerate(lens):
+        pages = table[slots[b], :-(-L // page)].long()
+        lo = max(0, L - window) if window > 0 else 0
+        for h in range(H):
+            keys = k[pages, h // (H // Hkv)].reshape(-1, hd)[lo:L]
+            vals = v[pages, h // (H // Hkv)].reshape(-1, hd)[lo:L]
+            p = torch.softmax(keys @ q[b, h * hd:(h + 1) * hd] * scale, dim=0)
+            out[b, h * hd:(h + 1) * hd] = p @ vals
+    return out
+
+
+def test_calls_in_a_row_equal_the_allocating_entry_point_and_float64(lib):
     H, Hkv, hd, page = 32, 8, 64, 64
     scale = hd ** -0.5
-    cases = [(make_case(1, [700, 33, 1500, 64, 1], H, Hkv, hd, page), 0, 6, 256),
-             (make_case(2, [90, 300], H, Hkv, hd, page), 128, 3, 128),      # smaller: stale partials lie behind it
-             (make_case(3, [257], H, Hkv, hd, page), 0, 1, 0)]              # one chunk: no scratch at all
-    for c, window, splits, keys in cases:
-        rc, got = call(lib, c, H, Hkv, hd, page, window, scale, splits, keys)
-        assert rc == 0, lib.zk_attn_decode_noalloc_error().decode()
+    cases = [([700, 33, 1500, 64, 1], 0, 6, 256),
+             ([90, 300], 128, 3, 128),          # smaller: stale partials of the call before lie behind it
+             ([257], 0, 1, 0)]                  # one chunk: no scratch at all
+    for seed, (lens, window, splits, keys) in enumerate(cases):
+        c = make_case(seed + 1, lens, H, Hkv, hd, page)
         ref = regular(c, H, Hkv, hd, window, scale, splits, keys)
+        f64 = exact(c, lens, H, Hkv, hd, page, window, scale)
         torch.cuda.synchronize()
-        err = (got.double() - ref.double()).abs().max().item() / ref.double().abs().max().item()
-        assert err <= 1.5e-2, f"window {window}, {splits} chunks: error {err:.3e}"
-        assert torch.isfinite(got.float()).all()
+        out = torch.empty_like(c["q"])                 # the caller's output; counted before the call
+        in_use = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
+        rc = lib.zk_attn_decode_noalloc(c["q"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), out.data_ptr(),
+                                        c["seq_start"].data_ptr(), c["seq_slot"].data_ptr(), c["table"].data_ptr(),
+                                        c["table"].stride(0), c["B"], H, Hkv, hd, page, window, scale, splits, keys,
+                                        torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0, lib.zk_attn_decode_noalloc_error().decode()
+        if seed > 0:       # the first call on a device may load the library's kernels
+            assert (torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]) == in_use, "the call changed the memory in use"
+        assert torch.isfinite(out.float()).all()
+        # row by row: a long sequence's output is an average of many values and much smaller than
+        # a short one's, so each row is measured against its own size
+        for b in range(len(lens)):
+            for name, want in (("the allocating entry point", ref[b].double().cpu()), ("float64", f64[b])):
+                err = (out[b].double().cpu() - want).abs().max().item() / want.abs().max().item()
+                assert err <= 1.5e-2, f"sequence {b} of {lens}, window {window}, {splits} chunks, against {name}: error {err:.3e}"
 
 
 def test_sizes_beyond_the_scratch_are_refused_with_a_message(lib):

@@ -6,12 +6,17 @@ token ids and a model folder, so `-p` takes comma-separated ids and `-m` a folde
     zinfer_b200 -m FOLDER -p 1,2,3 -n 32 --temp 0
     zinfer_b200 -m FOLDER -f prompts.txt --temp 0.8 --top-k 40 --seed 7
     zinfer_b200 --random-weights CONFIG.json --write FOLDER --seed-weights 3
-    zinfer_b200 -m FOLDER --bench 512,64
+    zinfer_b200 -m FOLDER --bench 512,64 --batch-sizes 1,8
+    zinfer_b200 -m FOLDER -p 1,2,3 -n 8 --dump-logits logits.f32
+
+Ctrl-C ends a running generation at its next step and prints what was generated so far
+(src/main.zig:297-299, src/gen.zig:476-479); a second Ctrl-C ends the program.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import signal
 import sys
 import time
 from pathlib import Path
@@ -49,6 +54,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--stop", default=None, help="stop token ids (default: the model's eos ids)")
     ap.add_argument("--bench", default=None, metavar="PP,TG",
                     help="time a prompt of PP synthetic tokens and TG generated tokens (src/main.zig:669-699)")
+    ap.add_argument("--batch-sizes", default="1", metavar="B1,B2,...",
+                    help="with --bench: run it for each of these numbers of equal sequences (default 1)")
+    ap.add_argument("--dump-logits", metavar="PATH",
+                    help="write the logits at the last token of every prompt as little-endian float32 "
+                         "[prompts, vocab] before generating")
     ap.add_argument("--random-weights", metavar="CONFIG.json", help="write a model folder with random weights")
     ap.add_argument("--write", metavar="FOLDER", help="where --random-weights writes")
     ap.add_argument("--seed-weights", type=int, default=0)
@@ -83,11 +93,22 @@ def main(argv=None) -> int:
         print(f"model: {cfg.architecture} | dtype {args.dtype} | ctx {ctx} | vocab {cfg.vocab_size} | "
               f"load {1e3 * (time.perf_counter() - t0):.0f} ms", file=sys.stderr)
 
+    def on_sigint(signum, frame):
+        if engine.interrupt.is_set():
+            raise KeyboardInterrupt
+        engine.interrupt.set()
+
+    signal.signal(signal.SIGINT, on_sigint)
+
     if args.bench:
         pp, tg = (int(x) for x in args.bench.split(","))
-        toks = [(i * 7919 + 13) % cfg.vocab_size for i in range(pp)]   # src/main.zig:673
-        res = engine.generate([toks], max_new_tokens=tg, temp=0.0, stop_ids=[])
-        print(engine.stats.report())
+        for b in parse_ids(args.batch_sizes):
+            if b > args.max_batch:
+                print(f"error: --batch-sizes {b} exceeds --max-batch {args.max_batch}", file=sys.stderr)
+                return 2
+            toks = [[(i * 7919 + 13 + 31 * s) % cfg.vocab_size for i in range(pp)] for s in range(b)]   # src/main.zig:673
+            engine.generate(toks, max_new_tokens=tg, temp=0.0, stop_ids=[])
+            print(f"batch {b}: " + engine.stats.report())
         return 0
 
     prompts = []
@@ -105,6 +126,16 @@ def main(argv=None) -> int:
                             dry_range=args.dry_range, xtc_probability=args.xtc_probability,
                             xtc_threshold=args.xtc_threshold, xtc_min_keep=args.xtc_min_keep)
     stop = parse_ids(args.stop) if args.stop is not None else None
+    if args.dump_logits:
+        import numpy as np
+        rows = []
+        for i in range(0, len(prompts), args.max_batch):
+            slots = engine.start(len(prompts[i:i + args.max_batch]))
+            try:
+                rows.append(engine.step(slots, prompts[i:i + args.max_batch]).float().cpu().numpy())
+            finally:
+                engine.finish(slots)
+        np.concatenate(rows).astype("<f4").tofile(args.dump_logits)
     results = engine.generate(prompts, max_new_tokens=args.predict, sampling=params, stop_ids=stop)
     for r in results:
         print(" ".join(str(t) for t in r.tokens) + f"  [{r.finish_reason}]")

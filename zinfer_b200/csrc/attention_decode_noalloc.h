@@ -14,6 +14,11 @@
 // of it (nothing when num_splits == 1) and is refused with ZK_NOALLOC_TOO_LARGE if that is more.
 //
 // Rules for callers:
+//  * The chunks must cover the longest sequence: num_splits * split_keys >= seq_start[b] + 1 for
+//    every b (with num_splits == 1 all keys are one chunk, whatever their number).  The lengths
+//    live on the device, so the call cannot check this; keys beyond the last chunk would be
+//    left out of the result without an error.  A caller whose sequences grow keeps
+//    num_splits * split_keys ahead of them.
 //  * The first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress).  Make that first call outside any stream capture.
 //  * All calls on a device share the one array, and it keeps what the last call left in it.

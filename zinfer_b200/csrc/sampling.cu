@@ -45,8 +45,13 @@ struct Prefix {
   __device__ __forceinline__ bool has(unsigned key, int idx) const { return key > T || (key == T && idx <= cut); }
 };
 
+// Bin masses are summed as integers (units of 2^-40 of the largest probability), so that a sum
+// does not depend on the order in which the threads' atomic adds arrive: the same row and seed
+// give the same cut in every run.  A mass is at most 1, so 2^24 of them fit.
+constexpr float MASS_UNIT = 1099511627776.0f;    // 2^40
+
 struct Shared {
-  float fbins[256];
+  unsigned long long mbins[256];
   int ibins[256];
   float fred[32];
   int ired[32];
@@ -188,7 +193,7 @@ __device__ Prefix select_top_p(const float* row, int V, const Prefix& in, float 
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int b = threadIdx.x; b < 256; b += blockDim.x) {
       sh.ibins[b] = 0;
-      sh.fbins[b] = 0.f;
+      sh.mbins[b] = 0ull;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -196,7 +201,7 @@ __device__ Prefix select_top_p(const float* row, int V, const Prefix& in, float 
       const unsigned key = key_of(l);
       if ((key & mask) == prefix && in.has(key, i)) {
         atomicAdd(&sh.ibins[(key >> shift) & 255], 1);
-        atomicAdd(&sh.fbins[(key >> shift) & 255], expf(l - mx));
+        atomicAdd(&sh.mbins[(key >> shift) & 255], (unsigned long long)(expf(l - mx) * MASS_UNIT));
       }
     }
     __syncthreads();
@@ -206,8 +211,9 @@ __device__ Prefix select_top_p(const float* row, int V, const Prefix& in, float 
       for (int j = 255; j >= 0; --j)
         if (sh.ibins[j] > 0) lowest = j;
       for (; b > lowest; --b) {
-        if (sh.ibins[b] > 0 && acc + sh.fbins[b] >= target) break;
-        acc += sh.fbins[b];
+        const float mass = (float)sh.mbins[b] * (1.0f / MASS_UNIT);
+        if (sh.ibins[b] > 0 && acc + mass >= target) break;
+        acc += mass;
       }
       sh.ival = b;
       sh.fval = target - acc;

@@ -10,6 +10,7 @@ sequences of unequal length are packed, not padded.
 """
 from __future__ import annotations
 
+import threading
 from collections import OrderedDict
 from typing import Optional, Sequence
 
@@ -128,6 +129,7 @@ class Engine:
         self._graphs: "OrderedDict[tuple, torch.cuda.CUDAGraph]" = OrderedDict()
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self.graph_captures = 0         # steps that were recorded instead of replayed, since the engine was built
+        self.interrupt = threading.Event()   # set it (from a signal handler, another thread, a callback) to end `generate`
         self.stats = None
 
     # ------------------------------------------------------------------ sequences
@@ -356,7 +358,9 @@ class Engine:
         """Generates for every prompt (a list of token ids each); returns a GenerationResult per
         prompt, in order.  `sampling` is a SamplingParams, or give its fields as keyword
         arguments (temp, top_k, top_p, min_p, repeat_penalty, seed, ...; `temperature` is
-        accepted for `temp`).  stop_ids default to the configuration's eos token ids."""
+        accepted for `temp`).  stop_ids default to the configuration's eos token ids.
+        Setting `self.interrupt` while it runs ends it at the next step: requests come back with
+        the tokens they have and the reason "interrupted" (the flag is cleared when a call starts)."""
         from ..sampling.sampler import Sampler, SamplingParams
         from .generate import GenerationLoop
 
@@ -369,8 +373,9 @@ class Engine:
         if stop_ids is None:
             stop_ids = self.model.config.eos_token_ids
         sampler = Sampler(sampling, self.vocab_size, len(prompts), self.device)
+        self.interrupt.clear()
         loop = GenerationLoop(self, self.cache.max_slots, self.cache.num_pages * self.cache.page_size,
-                              self.max_seq_len, self.cache.page_size)
+                              self.max_seq_len, self.cache.page_size, interrupt=self.interrupt)
         results = loop.run(prompts, sampler, max_new_tokens, stop_ids, on_step)
         self.stats = loop.stats
         return results

@@ -8,11 +8,18 @@ prompt in one step), then each live request goes on by one token a step; a reque
 leaves the batch, the others go on; when the batch has ended its slots go back to the cache and
 the next batch starts, until every request is served.
 
+The reference polls an atomic `interrupted` flag once per token and ends the generation there,
+keeping what it has (src/gen.zig:476-479; the command line sets it on Ctrl-C, src/main.zig:297-299).
+Here `interrupt` is a `threading.Event`: once it is set the loop ends every running request with
+the reason "interrupted" and the tokens it has so far, starts no further batch (requests that
+never ran come back empty with the same reason), and gives the slots back.
+
 The loop talks to a backend with five methods (`start`, `finish`, `prefill`, `decode`,
 `read_tokens`), so its decisions can be tested without a GPU.
 """
 from __future__ import annotations
 
+import threading
 import time
 
 import torch
@@ -23,7 +30,9 @@ from typing import Callable, Optional, Sequence
 @dataclass
 class GenerationResult:
     tokens: list[int]
-    finish_reason: str            # "stop" (a stop token was sampled), "length" (max_new_tokens), "context" (cache full)
+    # "stop" (a stop token was sampled), "length" (max_new_tokens), "context" (cache full),
+    # "interrupted" (the caller asked the loop to end: what was generated so far is returned)
+    finish_reason: str
     prompt_tokens: int
     stop_token: Optional[int] = None
 
@@ -78,10 +87,21 @@ def plan_batch(pending: Sequence[int], prompt_lens: Sequence[int], budgets: Sequ
 
 
 class GenerationLoop:
-    def __init__(self, backend, max_batch: int, max_tokens: int, max_seq_len: int, page_size: int):
+    def __init__(self, backend, max_batch: int, max_tokens: int, max_seq_len: int, page_size: int,
+                 interrupt: Optional[threading.Event] = None):
         self.backend = backend
         self.max_batch, self.max_tokens, self.max_seq_len, self.page_size = max_batch, max_tokens, max_seq_len, page_size
+        self.interrupt = interrupt if interrupt is not None else threading.Event()
         self.stats = Stats()
+
+    def _interrupted(self, active, out, results, lens) -> bool:
+        """Polled once per step: ends the running requests with what they have."""
+        if not self.interrupt.is_set():
+            return False
+        for r in active:
+            if results[r] is None:
+                results[r] = GenerationResult(out[r], "interrupted", lens[r])
+        return True
 
     def run(self, prompts: Sequence[Sequence[int]], sampler, max_new_tokens: int = 256,
             stop_ids: Sequence[int] = (), on_step: Optional[Callable[[dict[int, int]], None]] = None
@@ -108,6 +128,10 @@ class GenerationLoop:
         pending = list(range(n))
         be = self.backend
         while pending:
+            if self.interrupt.is_set():
+                for r in pending:
+                    results[r] = GenerationResult([], "interrupted", lens[r])
+                break
             batch = plan_batch(pending, lens, budgets, self.max_batch, self.max_tokens, self.page_size)
             pending = pending[len(batch):]
             self.stats.n_batches += 1
@@ -149,7 +173,7 @@ class GenerationLoop:
                         feed.append(tok)
                     if on_step is not None and emitted:
                         on_step(emitted)
-                    if not live:
+                    if not live or self._interrupted(live, out, results, lens):
                         break
                     logits = be.decode([slot_of[r] for r in live], feed)
                     toks = be.read_tokens(sampler.sample(logits, live))
@@ -201,7 +225,7 @@ class GenerationLoop:
                 live.append(r)
             if on_step is not None and emitted:
                 on_step(emitted)
-            if not live:
+            if not live or self._interrupted(live, out, results, lens):
                 if nxt_pending is not None:
                     nxt_pending.wait()      # nothing of the step that ran ahead is used
                 return
