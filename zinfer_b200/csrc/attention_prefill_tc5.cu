@@ -5,18 +5,30 @@
 // GP heads of the group packed beside each other (the reference orders the queries of a KV head the
 // same way, src/model.zig:1352-1366), and walks the keys in tiles of 64 that lie inside one cache
 // page.  Roles:
-//   * warp 4 (one lane) is the producer: one 3-D TMA load brings the 128 x 64 query tile, then per
+//   * warp 8 (one lane) is the producer: one 3-D TMA load brings the 128 x 64 query tile, then per
 //     key tile two 2-D TMA loads bring K and V ([64 keys, 64] each, 128-byte swizzle) into a ring of
-//     two stages;
-//   * warp 5 (one lane) issues tcgen05.mma: S = Q K^T (M 128, N 64 keys, four k steps; K is the
+//     four stages, so that the loads run three tiles ahead of the MMAs;
+//   * warp 9 (one lane) issues tcgen05.mma: S = Q K^T (M 128, N 64 keys, four k steps; K is the
 //     K-major B operand) into one of two score buffers in tensor memory, and O += P V (N 64 columns,
 //     four k steps over the 64 keys; V as it lies in the cache is the MN-major B operand);
-//   * warps 0..3 are the softmax: thread r owns row r of the tile, reads its 64 scores with
-//     tcgen05.ld, applies scale and the causal mask, keeps the running maximum and sum of the online
-//     softmax (src/attention.zig:478-517, no tile skipped), rescales its row of O in tensor memory,
-//     and writes its row of P as bfloat16 into the shared-memory tile that is the A operand of P V.
-// One block needs 128 columns of tensor memory and 65 KB of shared memory, so three blocks share an
-// SM and their softmax phases overlap one another's MMAs.  Scores stay unscaled in registers; the
+//   * warps 0..7 are the softmax, two threads per row: threads r and r + 128 own row r of the tile
+//     (a warp reaches the 32 accumulator lanes 32 (w mod 4) .., so warps w and w + 4 share rows),
+//     the first the scores of keys 0..31 of the tile and columns 0..31 of O, the second the other
+//     halves.  Each reads its 32 scores with tcgen05.ld, applies the causal mask, the two exchange
+//     their maxima through shared memory (a named barrier per pair of warps), keep the running
+//     maximum and their halves of the sum of the online softmax (src/attention.zig:478-517, no tile
+//     skipped), rescale their halves of the row of O in tensor memory and write their halves of the
+//     row of P as bfloat16 into the shared-memory tile that is the A operand of P V.  A row's chain
+//     of dependent operations per key tile is half as long as with one thread, which is what bounds
+//     a block (its tiles form one chain softmax -> P V -> Q K^T -> softmax).
+// The scores have two buffers in tensor memory: Q K^T of tile t + 1 is issued before the MMA warp waits
+// for P of tile t, so it runs while the softmax warps work on tile t, and P V of tile t runs while they
+// work on tile t + 1.  One block needs 256 columns of tensor memory (two score buffers and O) and 99 KB
+// of shared memory, so two blocks share an SM.  Measured on a B200 for 32 heads on 8 KV heads: a
+// prompt of 8,192 tokens 832 -> 577 us a layer (476 TFLOP/s), of 2,048 tokens 90 -> 72 us, against the
+// version with one thread per row, one score buffer and two K/V stages.  (Computing a part of the
+// exponentials by polynomial on the FMA pipe, beside ex2.approx, made it slower: the softmax warps are
+// bound by instruction issue, not by the special-function unit.)  Scores stay unscaled in registers; the
 // scale is folded into the exponent (2^((s - m) * scale * log2 e), ex2.approx), tiles below the
 // diagonal skip the mask, and a warp whose rows keep their maximum skips the rescaling of O.
 //
@@ -35,10 +47,13 @@ using namespace tc5;
 constexpr int HD = 64;            // head size
 constexpr int ROWS = 128;         // query rows per block = accumulator lanes
 constexpr int TK = 64;            // keys per tile
-constexpr int THREADS = 192;      // four softmax warps, producer warp, MMA warp
+constexpr int SM_THREADS = 256;   // eight softmax warps: two threads per row
+constexpr int THREADS = SM_THREADS + 64;   // then the producer warp and the MMA warp
 constexpr int Q_BYTES = ROWS * HD * 2, KV_BYTES = TK * HD * 2, P_BYTES = ROWS * TK * 2;
-constexpr size_t SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr unsigned TMEM_COLS = 128;   // S at column 0, O at column 64: three blocks fit an SM (by shared memory)
+constexpr int XCH_BYTES = 2 * 2 * ROWS * 4;   // the halves' maxima, double-buffered (the sums reuse it at the end)
+constexpr int NSTG = 4;           // K/V tiles in shared memory: the loads run three tiles ahead of the MMAs
+constexpr size_t SMEM_BYTES = Q_BYTES + 2 * NSTG * KV_BYTES + P_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + XCH_BYTES;
+constexpr unsigned TMEM_COLS = 256;   // two score buffers at columns 0 and 64, O at column 128: two blocks fit an SM
 
 struct Params {
   bf16* out;
@@ -64,24 +79,27 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const unsigned*>(&t);
 }
 
-__global__ void __launch_bounds__(THREADS, 3)
+__global__ void __launch_bounds__(THREADS, 2)
     attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_sm = base;
-  unsigned char* k_sm[2] = {base + Q_BYTES, base + Q_BYTES + 2 * KV_BYTES};
-  unsigned char* v_sm[2] = {base + Q_BYTES + KV_BYTES, base + Q_BYTES + 3 * KV_BYTES};
-  unsigned char* p_sm = base + Q_BYTES + 4 * KV_BYTES;
+  unsigned char* kv_sm = base + Q_BYTES;          // stage s: K at kv_sm + 2 s KV_BYTES, V behind it
+  auto k_sm = [&](int s) { return kv_sm + 2 * s * KV_BYTES; };
+  auto v_sm = [&](int s) { return kv_sm + (2 * s + 1) * KV_BYTES; };
+  unsigned char* p_sm = base + Q_BYTES + 2 * NSTG * KV_BYTES;
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_sm + P_BYTES);
   unsigned long long* q_full = bars;            // 1
-  unsigned long long* kv_full = bars + 1;       // [2]
-  unsigned long long* kv_empty = bars + 3;      // [2]
-  unsigned long long* s_full = bars + 5;        // 1 (bars + 6 unused)
-  unsigned long long* p_ready = bars + 7;       // 1, 128 arrivals
-  unsigned long long* pv_done = bars + 8;       // 1
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 9);
+  unsigned long long* kv_full = bars + 1;               // [NSTG]
+  unsigned long long* kv_empty = bars + 1 + NSTG;       // [NSTG]
+  unsigned long long* s_full = bars + 1 + 2 * NSTG;     // [2]: one per score buffer
+  unsigned long long* p_ready = bars + 3 + 2 * NSTG;    // 1, an arrival per softmax thread
+  unsigned long long* pv_done = bars + 4 + 2 * NSTG;    // 1
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 5 + 2 * NSTG);
+  static_assert((5 + 2 * NSTG) * 8 + 16 <= 256, "the barriers fit their 256 bytes");
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile float* xch = reinterpret_cast<volatile float*>(p_sm + P_BYTES + 256);   // [2 buffers][2 halves][ROWS]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int GP = p.gp, G = p.H / p.Hkv, chunks = G / GP;
@@ -98,36 +116,37 @@ __global__ void __launch_bounds__(THREADS, 3)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NSTG; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(p_ready, SM_THREADS);
     mbar_init(pv_done, 1);
     *aborted = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
   }
-  if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 9) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  const unsigned tmem_o = tmem_base + 64;
+  const unsigned tmem_o = tmem_base + 128;
   // Barriers and tensor memory are set up while the kernel before this one ends; q and the cache
   // are its results.  (The batch's index arrays read above were uploaded before the step began.)
   zk_let_next_start();
   zk_wait_prior();
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     // ---------------------------------------------------------------- producer
     const int* pt = p.page_table + (size_t)p.seq_slot[b] * p.pt_stride;
     mbar_expect_tx(q_full, Q_BYTES);
     tma_load_3d(q_sm, &map_q, 0, kvh * G + chunk * GP, t_base + q0, q_full);
     for (int t = 0; t < n_tiles; ++t) {
-      const int s = t & 1;
-      if (!mbar_wait(&kv_empty[s], ((t >> 1) & 1) ^ 1)) {
+      const int s = t % NSTG;
+      if (!mbar_wait(&kv_empty[s], ((t / NSTG) & 1) ^ 1)) {
         atomicExch(p.status, 14);
         *aborted = 1;
         break;
@@ -142,87 +161,102 @@ __global__ void __launch_bounds__(THREADS, 3)
       }
       const int row = (page * p.Hkv + kvh) * p.page_size + kb % p.page_size;
       mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
-      tma_load_2d(k_sm[s], &map_k, 0, row, &kv_full[s]);
-      tma_load_2d(v_sm[s], &map_v, 0, row, &kv_full[s]);
+      tma_load_2d(k_sm(s), &map_k, 0, row, &kv_full[s]);
+      tma_load_2d(v_sm(s), &map_v, 0, row, &kv_full[s]);
     }
-  } else if (warp == 5 && lane == 0) {
+  } else if (warp == 9 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
     const unsigned idesc_s = instr_desc(ROWS, TK);                    // Q [128 x 64] . K^T: both K-major
     const unsigned idesc_o = instr_desc(ROWS, HD) | (1u << 16);       // P [128 x 64 keys] . V: V is MN-major
     bool ok = mbar_wait(q_full, 0);
     if (!ok) atomicExch(p.status, 15);
     auto issue_s = [&](int t) {
-      const int s = t & 1;
-      if (!mbar_wait(&kv_full[s], (t >> 1) & 1)) {
+      const int s = t % NSTG, sb = t & 1;   // the K/V stage; the score buffer
+      if (!mbar_wait(&kv_full[s], (t / NSTG) & 1)) {
         atomicExch(p.status, 15);
         return false;
       }
       tc_fence_after();
-      const unsigned long long dq = smem_desc(q_sm), dk = smem_desc(k_sm[s]);
+      const unsigned long long dq = smem_desc(q_sm), dk = smem_desc(k_sm(s));
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)   // 32 bytes further along the swizzled rows per k step
-        umma_bf16(tmem_base, dq + (unsigned long long)(2 * k), dk + (unsigned long long)(2 * k), idesc_s,
-                  k > 0 ? 1u : 0u);
-      umma_commit(s_full);
+        umma_bf16(tmem_base + 64u * (unsigned)sb, dq + (unsigned long long)(2 * k), dk + (unsigned long long)(2 * k),
+                  idesc_s, k > 0 ? 1u : 0u);
+      umma_commit(&s_full[sb]);
       return true;
     };
     if (ok && n_tiles > 0) ok = issue_s(0);
     for (int t = 0; t < n_tiles && ok && !*aborted; ++t) {
+      // The scores of the next tile are computed while the softmax warps work on this one: they go to the
+      // other score buffer, whose last scores (tile t - 1) were read before P of that tile was announced.
+      if (t + 1 < n_tiles) {
+        ok = issue_s(t + 1);
+        if (!ok) break;
+      }
       if (!mbar_wait(p_ready, t & 1)) {               // the scores are read, P of tile t is in shared memory, O is rescaled
         atomicExch(p.status, 16);
         ok = false;
         break;
       }
       tc_fence_after();
-      const unsigned long long dp = smem_desc(p_sm), dv = smem_desc(v_sm[t & 1]);
+      const unsigned long long dp = smem_desc(p_sm), dv = smem_desc(v_sm(t % NSTG));
 #pragma unroll
       for (int k = 0; k < TK / 16; ++k)   // P: 32 bytes along its rows; V: 16 key rows of 128 bytes further
         umma_bf16(tmem_o, dp + (unsigned long long)(2 * k), dv + (unsigned long long)(128 * k), idesc_o,
                   (t > 0 || k > 0) ? 1u : 0u);
-      umma_commit(&kv_empty[t & 1]);
+      umma_commit(&kv_empty[t % NSTG]);
       umma_commit(pv_done);
-      if (t + 1 < n_tiles) ok = issue_s(t + 1);
     }
     if (!ok) *aborted = 1;
-  } else if (warp < 4) {
+  } else if (warp < 8) {
     // ---------------------------------------------------------------- softmax and epilogue
-    const int r = threadIdx.x;                       // row of the tile = accumulator lane
+    constexpr int HK = TK / 2, HO = HD / 2;         // a thread's keys of a tile, its columns of O
+    const int half = warp >> 2;                     // 0: keys 0..31 of a tile, columns 0..31 of O; 1: the others
+    const int r = threadIdx.x & (ROWS - 1);         // row of the tile = accumulator lane
     const int tq = r / GP, hl = r % GP;
     const bool row_ok = q0 + tq < Tq;
     const int row_hi = start + q0 + tq + 1;          // this row sees keys [0, row_hi)
-    const unsigned lane_sel = (unsigned)(warp * 32) << 16;
+    const unsigned lane_sel = (unsigned)((warp & 3) * 32) << 16;
+    const int pair_bar = 1 + (warp & 3);             // named barrier of the two warps that share these rows
     // scores are kept raw; the scale goes into the exponent: p = 2^((s - m) * scale * log2(e))
     const float c2 = p.scale * 1.4426950408889634f;
     const int all_visible = start + q0 + 1;          // keys below this are visible to every row of the tile
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;            // l_run: the sum over this thread's keys only
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
-      const int s = t & 1, kb = t * TK;
+      const int s = t & 1, kb = t * TK + half * HK;
       // (a warp decides as one: the tensor-memory loads and stores below are warp-collective)
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, t & 1));
-      if (!ok || *aborted) {
-        if (!ok) atomicExch(p.status, 17);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (t >> 1) & 1));
+      if (!ok) {
+        atomicExch(p.status, 17);
         *aborted = 1;
-        ok = false;
         break;
       }
       tc_fence_after();
-      float sc[TK];
+      float sc[HK];
 #pragma unroll
-      for (int c0 = 0; c0 < TK; c0 += 16) tmem_ld16(tmem_base + lane_sel + (unsigned)c0, sc + c0);
-      if (kb + TK > all_visible || !row_ok) {          // a tile on the diagonal (or a row that does not exist): mask
+      for (int c0 = 0; c0 < HK; c0 += 16) tmem_ld16(tmem_base + 64u * (unsigned)s + lane_sel + (unsigned)(half * HK + c0), sc + c0);
+      if (kb + HK > all_visible || !row_ok) {          // a tile on the diagonal (or a row that does not exist): mask
 #pragma unroll
-        for (int j = 0; j < TK; ++j) sc[j] = (row_ok && kb + j < row_hi) ? sc[j] : -INFINITY;
+        for (int j = 0; j < HK; ++j) sc[j] = (row_ok && kb + j < row_hi) ? sc[j] : -INFINITY;
       }
-      float m_new = m_run;
+      float m_mine = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < TK; ++j) m_new = fmaxf(m_new, sc[j]);
+      for (int j = 0; j < HK; ++j) m_mine = fmaxf(m_mine, sc[j]);
+      // the row's maximum over both halves
+      // (the two warps of a row leave this loop only where a bounded wait on a barrier they both wait for
+      // ran out, so neither can be left alone at the named barrier below)
+      volatile float* xm = xch + (t & 1) * 2 * ROWS;   // the buffers alternate: a value is read before it is replaced
+      xm[half * ROWS + r] = m_mine;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      const float m_other = xm[(half ^ 1) * ROWS + r];
+      const float m_new = fmaxf(m_run, fmaxf(m_mine, m_other));
       const float mc = m_new == -INFINITY ? 0.f : m_new * c2;
       const float alpha = ex2((m_run == -INFINITY ? -INFINITY : m_run * c2) - mc);
       float row_sum = 0.f;
-      unsigned pk[TK / 2];
+      unsigned pk[HK / 2];
 #pragma unroll
-      for (int j = 0; j < TK; j += 2) {
+      for (int j = 0; j < HK; j += 2) {
         const float p0 = ex2(fmaf(sc[j], c2, -mc)), p1 = ex2(fmaf(sc[j + 1], c2, -mc));
         row_sum += p0 + p1;
         pk[j / 2] = pack_bf16(p0, p1);
@@ -241,25 +275,25 @@ __global__ void __launch_bounds__(THREADS, 3)
         tc_fence_after();
         if (__any_sync(0xffffffffu, rescale)) {        // no row of the warp has a new maximum: O stays
 #pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 16) {
+          for (int c0 = 0; c0 < HO; c0 += 16) {
             float o[16];
-            tmem_ld16(tmem_o + lane_sel + (unsigned)c0, o);
+            tmem_ld16(tmem_o + lane_sel + (unsigned)(half * HO + c0), o);
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] *= alpha;
-            tmem_st16(tmem_o + lane_sel + (unsigned)c0, o);
+            tmem_st16(tmem_o + lane_sel + (unsigned)(half * HO + c0), o);
           }
         }
       }
-      // this row of P: 8 chunks of 8 keys, chunk c at the swizzled place (c ^ (r & 7))
+      // this thread's half of the row of P: 4 chunks of 8 keys, chunk c at the swizzled place (c ^ (r & 7))
 #pragma unroll
-      for (int c = 0; c < TK / 8; ++c)
-        *reinterpret_cast<uint4*>(p_sm + r * 128 + ((c ^ (r & 7)) * 16)) =
+      for (int c = 0; c < HK / 8; ++c)
+        *reinterpret_cast<uint4*>(p_sm + r * 128 + (((half * (HK / 8) + c) ^ (r & 7)) * 16)) =
             make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       // rows of V beyond the last key of the sequence's step hold stale cache contents
-      if (kb + TK > k_end) {
-        const int first = k_end - kb;   // 1 .. 63
-        for (int i = threadIdx.x; i < (TK - first) * 8; i += 128)
-          *reinterpret_cast<uint4*>(v_sm[s] + (first + i / 8) * 128 + (i % 8) * 16) = make_uint4(0, 0, 0, 0);
+      if (t * TK + TK > k_end) {
+        const int first = k_end - t * TK;   // 1 .. 63
+        for (int i = threadIdx.x; i < (TK - first) * 8; i += SM_THREADS)
+          *reinterpret_cast<uint4*>(v_sm(t % NSTG) + (first + i / 8) * 128 + (i % 8) * 16) = make_uint4(0, 0, 0, 0);
       }
       fence_async_smem();
       tc_fence_before();
@@ -271,13 +305,20 @@ __global__ void __launch_bounds__(THREADS, 3)
       *aborted = 1;
     }
     tc_fence_after();
-    if (ok) {   // uniform in the warp: every lane reads its row of O, the rows that exist store it
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      bf16* dst = p.out + (size_t)(t_base + min(q0 + tq, Tq - 1)) * p.H * HD + (size_t)(kvh * G + chunk * GP + hl) * HD;
+    if (ok) {   // uniform in the warp: every lane reads its half of its row of O, the rows that exist store it
+      // the row's sum is the two halves' sums (both ran with the same maxima)
+      volatile float* xs = xch + (n_tiles & 1) * 2 * ROWS;
+      xs[half * ROWS + r] = l_run;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      const float l_other = xs[(half ^ 1) * ROWS + r];
+      const float l_row = half == 0 ? l_run + l_other : l_other + l_run;   // first half + second half, in both threads
+      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+      bf16* dst = p.out + (size_t)(t_base + min(q0 + tq, Tq - 1)) * p.H * HD + (size_t)(kvh * G + chunk * GP + hl) * HD +
+                  half * HO;
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 16) {
+      for (int c0 = 0; c0 < HO; c0 += 16) {
         float o[16];
-        tmem_ld16(tmem_o + lane_sel + (unsigned)c0, o);
+        tmem_ld16(tmem_o + lane_sel + (unsigned)(half * HO + c0), o);
         uint4 w0, w1;
         w0.x = pack_bf16(o[0] * inv, o[1] * inv);   w0.y = pack_bf16(o[2] * inv, o[3] * inv);
         w0.z = pack_bf16(o[4] * inv, o[5] * inv);   w0.w = pack_bf16(o[6] * inv, o[7] * inv);
@@ -293,7 +334,7 @@ __global__ void __launch_bounds__(THREADS, 3)
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 9) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
