@@ -169,9 +169,9 @@ def time_decode(engine, torch, rng, batch: int, steps: int, warmup: int, vocab: 
     return ms, cached, launches, captures
 
 
-def time_prefill(engine, torch, rng, cfg, warmup: int, num: dict, pk: dict) -> dict:
-    """One sequence of PREFILL_TOKENS tokens in one step; median of 5 after the warm-up."""
-    toks = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
+def time_prefill(engine, torch, rng, cfg, warmup: int, num: dict, pk: dict, tokens: int = PREFILL_TOKENS) -> dict:
+    """One sequence of `tokens` tokens in one step; median of 5 after the warm-up."""
+    toks = rng.integers(0, cfg.vocab_size, size=tokens).tolist()
     times = []
     for i in range(warmup + 5):
         slot = engine.start(1)
@@ -185,7 +185,7 @@ def time_prefill(engine, torch, rng, cfg, warmup: int, num: dict, pk: dict) -> d
         if i >= warmup:
             times.append(start.elapsed_time(stop))
     pre_ms = statistics.median(times)
-    T = PREFILL_TOKENS
+    T = tokens
     flops = 2 * T * num["layer_params"] + 2 * num["head_params"] + num["n_attn"] * 2 * T * T * cfg.q_dim
     return {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
             "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
@@ -249,11 +249,12 @@ def own_arm(args) -> dict:
     cfg = z.config_from_dict(cfg_dict)
     model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True)
     B = args.batch
-    engine = z.Engine(model, max_batch=64, max_seq_len=CONTEXT, max_tokens=64 * CONTEXT, page_size=64,
+    engine = z.Engine(model, max_batch=64, max_seq_len=max(CONTEXT, args.prefill_tokens), page_size=64,
+                      max_tokens=max(64 * CONTEXT, args.prefill_tokens), max_step_tokens=max(8192, args.prefill_tokens),
                       use_graphs=not args.no_graphs)
     if args.only == "prefill":
         return {"prefill": time_prefill(engine, torch, np.random.default_rng(0), cfg, args.warmup,
-                                        model_numbers(cfg, cfg.num_hidden_layers), pk)}
+                                        model_numbers(cfg, cfg.num_hidden_layers), pk, args.prefill_tokens)}
     rng = np.random.default_rng(0)
     num = model_numbers(cfg, cfg.num_hidden_layers)
     weight_bytes = 2 * (num["layer_params"] + num["head_params"])
@@ -285,7 +286,7 @@ def own_arm(args) -> dict:
     # the same metric end to end through the public entry point: host token ids in and out every step
     prompts = [rng.integers(0, cfg.vocab_size, size=int(n)).tolist()
                for n in rng.integers(PROMPT_RANGE[0], PROMPT_RANGE[1] + 1, size=B)]
-    n_new = args.steps + 1
+    n_new = max(POINT_STEPS, args.steps) + 1       # at least 64 steps, as the other points
     # warm-up: the same generation once, so that every graph the timed one replays is captured
     engine.generate(prompts, max_new_tokens=n_new, temp=0.0, stop_ids=[])
     engine.generate(prompts, max_new_tokens=n_new, temp=0.0, stop_ids=[])
@@ -329,6 +330,8 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only (for profiling); the JSON line then lacks the other parts")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="with --only prefill: the prompt's length (the headline line always uses 2,048)")
     ap.add_argument("--model", default="1.2b", choices=["1.2b"] + sorted(SECONDARY),
                     help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only)")
     args = ap.parse_args()

@@ -256,15 +256,32 @@ __global__ void penalties_kernel(float* __restrict__ logits, int V, const int* _
     }
 }
 
-// Lowest index among the largest logits of each row (src/sampler.zig:532-610).
-__global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+// Lowest index among the largest logits of each row (src/sampler.zig:532-610).  `feed`, if given, gets
+// the same indices (the token slots of the next step's batch description); `status`, if given, is
+// copied behind the n indices of `out`, so that one device-to-host copy brings tokens and status.
+// A row is cut into gridDim.y pieces, a block each: a block folds its best (value, index) into a
+// 64-bit key, larger value first and lower index second, and takes the maximum into the row's word of
+// `keys`; the block that finds itself the last of all writes the tokens and leaves the keys and the
+// counter zero for the next launch.  The result does not depend on the order of the blocks.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+  unsigned u = __float_as_uint(v);
+  u = (v != v) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));   // ordered as the values; NaN lowest
+  return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)idx);
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out, int* __restrict__ feed,
+                              const int* __restrict__ status, unsigned long long* __restrict__ keys,
+                              unsigned* __restrict__ counter) {
   __shared__ Shared sh;
+  __shared__ int sm_last;
   zk_let_next_start();
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
+  const int n = gridDim.x, pieces = gridDim.y;
   const float* row = logits + (size_t)blockIdx.x * V;
+  const int per = (V + pieces - 1) / pieces, lo = blockIdx.y * per, hi = min(V, lo + per);
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     float v = row[i];
     if (v != v) v = -INFINITY;
     if (v > best || (v == best && i < best_i)) {
@@ -274,7 +291,26 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
   }
   const float mx = block_reduce_max(best, sh);
   const int idx = block_reduce_imin(best == mx ? best_i : 0x7fffffff, sh);
-  if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  if (threadIdx.x == 0) {
+    if (idx != 0x7fffffff) atomicMax(keys + blockIdx.x, argmax_key(mx, idx));
+    __threadfence();
+    sm_last = atomicAdd(counter, 1u) == (unsigned)(n * pieces - 1);
+  }
+  __syncthreads();
+  if (sm_last) {
+    __threadfence();
+    for (int r = threadIdx.x; r < n; r += blockDim.x) {
+      const unsigned long long k = __ldcg(keys + r);
+      const int tok = k ? (int)(0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull)) : 0;
+      out[r] = tok;
+      if (feed) feed[r] = tok;
+      keys[r] = 0ull;
+    }
+    if (threadIdx.x == 0) {
+      if (status) out[n] = *status;
+      *counter = 0u;
+    }
+  }
 }
 
 // One draw per row.  uniforms[row] = {u for the draw, u for the XTC chance}, both in [0, 1).
@@ -383,11 +419,17 @@ int zk_apply_penalties(float* logits, int n, int V, const int* rep_tokens, int R
   return ZK_LAUNCH_STATUS();
 }
 
-int zk_argmax(const float* logits, int n, int V, int* out, cudaStream_t stream) {
+// out [n] (or [n + 1] with `status`: out[n] = *status); feed [n] or null.  `scratch` holds n 64-bit keys
+// and, behind them, one 32-bit counter, all zero before the launch and again after it.
+int zk_argmax(const float* logits, int n, int V, int* out, int* feed, const int* status, void* scratch,
+              cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (V <= 0) return ZK_EINVAL;
-  argmax_kernel<<<n, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, V, out);
-  return ZK_LAUNCH_STATUS();
+  if (V <= 0 || !scratch) return ZK_EINVAL;
+  // a few SMs' worth of blocks per step: a row of 65,536 logits is cut into 16 pieces
+  const int pieces = V >= 16384 ? 16 : (V >= 4096 ? 4 : 1);
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(scratch);
+  return zk_launch_dependent(argmax_kernel, dim3(n, pieces), dim3(256), 0, stream, logits, V, out, feed, status, keys,
+                             reinterpret_cast<unsigned*>(keys + n));
 }
 
 int zk_sample(const float* logits, int n, int V, float temp, int top_k, float top_p, float min_p,

@@ -54,6 +54,10 @@ class _DecodeBatch:
         words = batch_layout(n_seqs, n_seqs)["_total"][0]
         self.meta_dev = torch.zeros(words, dtype=torch.int32, device=device)
         self.logits = torch.empty((n_seqs, vocab), dtype=torch.float32, device=device)
+        # every step ends with the arg-max of its logits: the n tokens and, behind them, the status word
+        self.greedy = torch.zeros(n_seqs + 1, dtype=torch.int32, device=device)
+        self.n_seqs = n_seqs
+        self._tail = batch_layout(n_seqs, n_seqs)["tok_seq"][0]      # where the description goes on behind the token ids
         self._hosts = [torch.zeros(words, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self._copied = [None] * self.RING
         self._next = 0
@@ -62,17 +66,24 @@ class _DecodeBatch:
 
     def upload(self, words, dev_tokens: Optional[torch.Tensor] = None) -> None:
         """Copies the packed batch description to the static device buffer; `dev_tokens`, if
-        given, then replaces its token ids (the first array of the description) on the device."""
+        given, then replaces its token ids (the first array of the description) on the device.
+        If `dev_tokens` are this batch's own greedy tokens of the step before, they already lie in
+        the token slots (the step's last kernel put them there): only the rest is copied."""
         i = self._next
         self._next = (i + 1) % self.RING
         if self._copied[i] is not None:
             self._copied[i].synchronize()
         self._hosts[i].numpy()[:] = words
-        self.meta_dev.copy_(self._hosts[i], non_blocking=True)
+        in_place = (dev_tokens is not None and dev_tokens.data_ptr() == self.greedy.data_ptr()
+                    and dev_tokens.numel() == self.n_seqs)
+        if in_place:
+            self.meta_dev[self._tail:].copy_(self._hosts[i][self._tail:], non_blocking=True)
+        else:
+            self.meta_dev.copy_(self._hosts[i], non_blocking=True)
         if self._copied[i] is None:
             self._copied[i] = torch.cuda.Event()
         self._copied[i].record()
-        if dev_tokens is not None:
+        if dev_tokens is not None and not in_place:
             self.meta_dev[:dev_tokens.numel()].copy_(dev_tokens)
 
 
@@ -129,6 +140,7 @@ class Engine:
         self._graphs: "OrderedDict[tuple, torch.cuda.CUDAGraph]" = OrderedDict()
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self.graph_captures = 0         # steps that were recorded instead of replayed, since the engine was built
+        self._host_ring, self._host_next = None, 0      # pinned buffers the sampled tokens are read into
         self.interrupt = threading.Event()   # set it (from a signal handler, another thread, a callback) to end `generate`
         self.stats = None
 
@@ -276,19 +288,36 @@ class Engine:
         """What a recorded single-token step is good for: the batch size and every mixer's launch key."""
         return (n_seqs, *(m.launch_key(n_seqs, longest) for m in self._key_mixers))
 
+    def _forward_single_tokens(self, ctx, batch: _DecodeBatch) -> None:
+        """The step's kernels: the model, then the arg-max of every row of logits.  The arg-max goes to
+        `batch.greedy` (with the status word behind it: one small copy brings both to the host) and into
+        the token slots of the batch description, where the next step of the same batch finds it."""
+        self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+        kernels.argmax(batch.logits, out=batch.greedy, feed=batch.meta_dev[:batch.n_seqs], status=self.status)
+
+    def greedy_tokens(self, logits: torch.Tensor) -> Optional[torch.Tensor]:
+        """If `logits` are what the last `decode` returned from a recorded (or warm-up) step: the int32
+        tensor [n + 1] with the arg-max token of every row and the status word behind them, computed by
+        the step itself.  Feeding its first n elements to the next `decode` of the same slots costs no
+        copy on the device.  None for logits of any other origin."""
+        for batch in self._decode_batches.values():
+            if batch.logits is logits:
+                return batch.greedy
+        return None
+
     def _decode_graph(self, batch: _DecodeBatch, B: int, longest: int) -> torch.Tensor:
         ctx = StepContext(self.dtype, self.device, self.status, batch.meta_dev, B, B, [1] * B, longest,
                           memo=batch.memo, sm_count=self.sm_count)
         if not batch.warmed:
             batch.warmed = True
-            self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+            self._forward_single_tokens(ctx, batch)
             return batch.logits
         key = self.decode_key(B, longest)
         graph = self._graphs.get(key)
         if graph is None:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+                self._forward_single_tokens(ctx, batch)
             self._graphs[key] = graph
             self.graph_captures += 1
             while len(self._graphs) > self.MAX_GRAPHS:
@@ -316,7 +345,7 @@ class Engine:
                                   length, memo=batch.memo, sm_count=self.sm_count)
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, pool=self._graph_pool):
-                    self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
+                    self._forward_single_tokens(ctx, batch)
                 self._graphs[key] = graph
                 self.graph_captures += 1
             if length >= longest:
@@ -343,11 +372,17 @@ class Engine:
             raise StepError(_STATUS_TEXT.get(both[-1], f"device status {both[-1]}"))
         return both[:-1]
 
-    def read_tokens_async(self, tokens: torch.Tensor):
+    def read_tokens_async(self, tokens: torch.Tensor, with_status: bool = False):
         """Starts copying sampled tokens (and the status word) to the host; the returned object's
-        `wait()` gives them once the copy has run, whatever was launched after it."""
-        both = torch.cat([tokens.to(torch.int32), self.status])
-        host = torch.empty(both.shape, dtype=torch.int32, pin_memory=True)
+        `wait()` gives them once the copy has run, whatever was launched after it.  `with_status`: the
+        tensor's last element already is the status word (`greedy_tokens`)."""
+        both = tokens if with_status else torch.cat([tokens.to(torch.int32), self.status])
+        ring = self._host_ring
+        if ring is None or ring[0].numel() < both.numel():
+            ring = self._host_ring = [torch.empty(max(both.numel(), self.cache.max_slots + 1), dtype=torch.int32,
+                                                  pin_memory=True) for _ in range(8)]
+        self._host_next = (self._host_next + 1) % len(ring)
+        host = ring[self._host_next][:both.numel()]     # at most two reads are under way at a time
         host.copy_(both, non_blocking=True)
         done = torch.cuda.Event()
         done.record()

@@ -193,6 +193,8 @@ class GenerationLoop:
         batch.  The tokens, their order and the reasons are those of the plain loop; the sampler
         must not need the host's history of a request."""
         pending, keep = None, None       # the copy of `toks_dev` under way, and which of its rows are `active`
+        # a backend whose steps end with the arg-max of their logits spares a greedy sampler its kernel
+        greedy = getattr(be, "greedy_tokens", None) if getattr(getattr(sampler, "p", None), "greedy", False) else None
         while True:
             # Requests that go on unless the token they are about to receive is a stop token.
             # Their step is launched now, on the device's copy of those tokens; the host reads
@@ -203,8 +205,13 @@ class GenerationLoop:
             if ahead:
                 feed = toks_dev if len(rows) == len(active) else toks_dev[torch.tensor(rows, device=toks_dev.device)]
                 logits = be.decode([slot_of[r] for r in ahead], feed)
-                nxt_dev = sampler.sample(logits, ahead)
-                nxt_pending = be.read_tokens_async(nxt_dev)
+                packed = greedy(logits) if greedy is not None else None
+                if packed is not None:      # the step computed its own arg-max; the status word lies behind it
+                    nxt_dev = packed[:len(ahead)]
+                    nxt_pending = be.read_tokens_async(packed, with_status=True)
+                else:
+                    nxt_dev = sampler.sample(logits, ahead)
+                    nxt_pending = be.read_tokens_async(nxt_dev)
                 self.stats.n_decode_steps += 1
             if pending is not None:
                 got = pending.wait()

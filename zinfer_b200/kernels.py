@@ -71,7 +71,7 @@ _SIGNATURES = {
     },
     "sampling": {
         "zk_apply_penalties": "piipifppip",
-        "zk_argmax": "piipp",
+        "zk_argmax": "piippppp",
         "zk_sample": "piififfffippp",
     },
     "attention": {
@@ -667,13 +667,35 @@ def apply_penalties(logits, rep_tokens, rep_penalty: float, dry_tokens, dry_pen)
                                                  _ptr(dry_tokens), _ptr(dry_pen), P, _stream()), "apply_penalties")
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
-    """Lowest index among the largest logits of each row; int32 [n]."""
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed: Optional[torch.Tensor] = None,
+           status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Lowest index among the largest logits of each row; int32 [n].  `out` may be given (with
+    `status` it has n + 1 words and the last receives the status word's value); `feed` [n] receives
+    the same indices (the next step's token slots)."""
     _need(logits, "logits", torch.float32, (None, None))
     n, V = logits.shape
-    out = torch.empty(n, dtype=torch.int32, device=logits.device)
-    _check(_fn("sampling", "zk_argmax")(_ptr(logits), n, V, _ptr(out), _stream()), "argmax")
+    if out is None:
+        out = torch.empty(n + (1 if status is not None else 0), dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, (n + (1 if status is not None else 0),))
+    if feed is not None:
+        _need(feed, "feed", torch.int32, (n,))
+    if status is not None:
+        _need(status, "status", torch.int32)
+    scratch = _argmax_scratch(logits.device, n)
+    _check(_fn("sampling", "zk_argmax")(_ptr(logits), n, V, _ptr(out), _ptr(feed), _ptr(status), _ptr(scratch),
+                                        _stream()), "argmax")
     return out
+
+
+def _argmax_scratch(device, n: int) -> torch.Tensor:
+    """Zeroed words in which the blocks of an arg-max meet (n 64-bit keys and a counter) and which the
+    kernel leaves zero again; one buffer per device, shared by launches that follow one another."""
+    dev = torch.device(device)
+    key = ("argmax scratch", dev.index if dev.index is not None else torch.cuda.current_device())
+    t = _device_state.get(key)
+    if t is None or t.numel() < n + 1:
+        t = _device_state[key] = torch.zeros(max(n + 1, 4097), dtype=torch.int64, device=dev)
+    return t
 
 
 def sample(logits, uniforms, temp: float, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
