@@ -203,7 +203,63 @@ def test_gemm_skinny_with_fused_norm(k, M, N, K):
     assert not k.gemm_skinny_takes(k.NormInput(rnd((17, K), 1, torch.float32).cuda(), nw, 1e-5), w)
 
 
-@pytest.mark.parametrize("M,F,K,norm", [(1, 208, 80, False), (8, 8192, 2048, True), (16, 144, 96, True), (5, 32, 64, False)])
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (8, 2048, 8192), (5, 5000, 64), (8, 16 * 148 * 6 + 24, 32), (3, 16, 8)])
+def test_gemm_skinny_writes_the_next_norms_inputs(k, M, N, K):
+    """The accumulating contraction into float32 rows also writes bfloat16(rows * norm weight) and the
+    rows' sums of squares per 16 columns: all three kernel shapes (few, some, many blocks), a ragged
+    last group of columns."""
+    a = rnd((M, K), 1, torch.bfloat16).cuda()
+    w = rnd((N, K), 2, torch.bfloat16, 0.1).cuda()
+    nw = (1 + rnd((N,), 3, torch.float32, 0.2)).cuda()
+    res0 = rnd((M, N), 4, torch.float32, 2.0).cuda()
+    res, plain = res0.clone(), res0.clone()
+    emit = k.NormEmit(nw)
+    assert k.gemm_skinny_emits(a, res)
+    k.gemm_skinny(a, w, out=res, accumulate=True, emit=emit)
+    k.gemm_skinny(a, w, out=plain, accumulate=True)
+    assert torch.equal(res, plain)                       # the sum itself is the same bits
+    assert emit.xw.shape == (M, N) and emit.ssq.shape == (M, -(-N // 16))
+    assert torch.equal(emit.xw, (res * nw).bfloat16())
+    sq = torch.zeros((M, emit.ssq.shape[1] * 16), dtype=torch.float64, device="cuda")
+    sq[:, :N] = res.double() ** 2
+    close(emit.ssq, sq.reshape(M, -1, 16).sum(-1), torch.float32, "sums of squares per 16 columns")
+    with pytest.raises(k.KernelError):
+        k.gemm_skinny(rnd((9, K), 1, torch.bfloat16).cuda(), w, out=rnd((9, N), 4, torch.float32).cuda(),
+                      accumulate=True, emit=k.NormEmit(nw))
+    with pytest.raises(k.KernelError):
+        k.gemm_skinny(a, w, out=res.bfloat16(), accumulate=True, emit=k.NormEmit(nw))
+
+
+def scaled_input(k, x, nw, eps, parts_of=16):
+    """What a contraction that summed into x would have left for the norm (nw, eps)."""
+    M, K = x.shape
+    sq = torch.zeros((M, -(-K // parts_of) * parts_of), dtype=torch.float32, device=x.device)
+    sq[:, :K] = x * x
+    return k.ScaledInput((x * nw).bfloat16(), sq.reshape(M, -1, parts_of).sum(-1).contiguous(), eps)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (8, 6144, 2048), (16, 100, 1000), (7, 65536 + 16, 72)])
+def test_gemm_skinny_with_prepared_norm(k, M, N, K):
+    x = rnd((M, K), 1, torch.float32, 3.0).cuda()
+    x[M - 1] *= 40.0                                    # a row whose scale differs much from the others'
+    nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
+    w = rnd((N, K), 3, torch.bfloat16, 0.1).cuda()
+    ref = norm_ref(x, nw, 1e-5).bfloat16().double() @ w.double().T
+    inp = scaled_input(k, x, nw, 1e-5)
+    assert k.gemm_skinny_takes(inp, w)
+    close(k.gemm_skinny(inp, w, out_dtype=torch.float32), ref, torch.bfloat16, "skinny + prepared norm")
+    for m in range(M):     # each row against its own size: a wrong row's scale would show
+        close(k.gemm_skinny(inp, w, out_dtype=torch.float32)[m], ref[m], torch.bfloat16, f"row {m}")
+    bias = rnd((N,), 5, torch.float32).cuda()
+    res0 = rnd((M, N), 4, torch.float32).cuda()
+    res = res0.clone()
+    k.gemm_skinny(inp, w, out=res, accumulate=True, bias=bias)
+    close(res, ref + bias.double() + res0.double(), torch.bfloat16, "prepared norm, bias, accumulate")
+    assert not k.gemm_skinny_takes(scaled_input(k, rnd((17, K), 1, torch.float32).cuda(), nw, 1e-5), w)
+
+
+@pytest.mark.parametrize("M,F,K,norm", [(1, 208, 80, False), (8, 8192, 2048, True), (16, 144, 96, True), (5, 32, 64, False),
+                                        (8, 8192, 2048, "prepared"), (3, 48, 72, "prepared"), (13, 144, 96, "prepared")])
 def test_gemm_skinny_swiglu(k, M, F, K, norm):
     halves = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
     w_mixed = interleaved([halves[:F], halves[F:]])
@@ -211,7 +267,8 @@ def test_gemm_skinny_swiglu(k, M, F, K, norm):
     if norm:
         x = rnd((M, K), 1, torch.float32, 2.0).cuda()
         nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
-        inp, a = k.NormInput(x, nw, 1e-6), norm_ref(x, nw, 1e-6).bfloat16().double()
+        inp = scaled_input(k, x, nw, 1e-6) if norm == "prepared" else k.NormInput(x, nw, 1e-6)
+        a = norm_ref(x, nw, 1e-6).bfloat16().double()
     else:
         inp = rnd((M, K), 1, torch.bfloat16).cuda()
         a = inp.double()
@@ -235,7 +292,8 @@ def test_gemm_tc_with_swiglu_epilogue(k, M, F, K):
 
 
 @pytest.mark.parametrize("M,D,K,taps,bias,norm", [(1, 80, 80, 2, False, False), (8, 2048, 2048, 3, False, True),
-                                                  (13, 96, 96, 4, True, True), (16, 48, 64, 7, True, False)])
+                                                  (13, 96, 96, 4, True, True), (16, 48, 64, 7, True, False),
+                                                  (8, 2048, 2048, 3, False, "prepared"), (5, 96, 104, 4, True, "prepared")])
 def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
     """Three fused single-token steps against in_proj + conv_decode, state included; in_proj's rows
     are stored as groups of 16 B, 16 C, 16 X rows for both paths."""
@@ -250,7 +308,8 @@ def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
     for step in range(3):
         x = rnd((M, K), 10 + step, torch.float32, 2.0).cuda()
         if norm:
-            inp, xn = k.NormInput(x, nw, 1e-5), k.rmsnorm(x, nw, 1e-5, torch.bfloat16)
+            inp = scaled_input(k, x, nw, 1e-5) if norm == "prepared" else k.NormInput(x, nw, 1e-5)
+            xn = k.rmsnorm(x, nw, 1e-5, torch.bfloat16)
         else:
             inp = xn = x.bfloat16()
         y_fused = k.gemm_skinny_conv(inp, w_in, in_b, st_a, tw, cb, slots)

@@ -146,3 +146,38 @@ def test_chunked_prompts_against_plain(model_folders, name, dtype, chunk):
             e = np.abs(more[i] - full[-1]).max() / np.abs(full).max()
             assert e <= helpers.tol(name, dtype), f"round {round_}: sequence {i}, the token after the prompt: error {e:.3e}"
     engine.cache.check_consistency()
+
+
+@pytest.mark.parametrize("name", ["loud_d", "loud_e"])
+def test_single_token_steps_of_few_sequences_prepare_their_norms(model_folders, name, monkeypatch):
+    """In bfloat16 steps of up to 8 rows the contraction that sums into the residual rows prepares the
+    norm that follows, for every norm of the step but the first (behind the embedding), the final
+    norm included.  The same steps with that route closed agree with the plain model as well."""
+    import zinfer_b200 as z
+    from zinfer_b200 import kernels
+    from zinfer_b200.parts.norm import RMSNorm
+    folder = model_folders[name]
+    plain = PlainLfm2(folder, dtype=np.float64)
+    vocab, n_layers = plain.cfg["vocab_size"], plain.cfg["num_hidden_layers"]
+    seqs = [helpers.random_tokens(900 + i, 9 + 3 * i + 6, vocab) for i in range(5)]
+    heads = [len(s) - 6 for s in seqs]
+    ref = [plain.logits(s) for s in seqs]
+    made = []
+
+    class Counted(kernels.ScaledInput):
+        def __init__(self, *a, **kw):
+            made.append(1)
+            super().__init__(*a, **kw)
+
+    monkeypatch.setattr(kernels, "ScaledInput", Counted)
+    counts = {}
+    for route in ("prepared", "closed"):
+        if route == "closed":
+            monkeypatch.setattr(RMSNorm, "ahead", lambda self, ctx, x: None)
+        engine = z.Engine(z.load(folder, dtype="bfloat16"), max_batch=5, max_seq_len=128, page_size=64, use_graphs=False)
+        made.clear()
+        worst, where, sizes = drive(engine, seqs, heads, ref)
+        counts[route] = len(made) / len(sizes)
+        print(f"{name} {route}: {counts[route]:.1f} prepared norms a single-token step, worst error {worst:.3e}")
+        assert worst <= helpers.tol(name, "bfloat16"), f"{route}: worst error {worst:.3e} at {where}"
+    assert counts["prepared"] == 2 * n_layers and counts["closed"] == 0, counts

@@ -15,16 +15,21 @@
 // as the kernel:
 //  * NORM: X is the float32 residual stream and the block applies RMSNorm itself
 //    (src/model.zig:1166-1181) while its first weights are in flight;
+//  * NORM_SCALED: the kernel that wrote the residual rows also wrote them as bfloat16(x * w) and
+//    their sums of squares per 16 columns (EMIT); this kernel reads those rows like any
+//    bfloat16 input and multiplies its float32 sums by the row's 1/rms: the norm costs no launch;
 //  * EPI_SWIGLU: the block owns gate rows f and up rows F + f and writes silu(g) * u
 //    (src/model.zig:1085-1117: gate, up and the activation in one worker);
 //  * EPI_CONV: the block owns rows ch, D + ch, 2D + ch of the short convolution's in_proj and
 //    runs the gated convolution with its state update on them (src/model.zig:2002-2020).
 #include "common.cuh"
 #include <stdlib.h>
+#include <type_traits>
 
 namespace {
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_CONV = 2 };
+enum { NORM_NONE = 0, NORM_FUSED = 1, NORM_SCALED = 2 };
 
 struct Args {
   const bf16* X;         // [M, K] bfloat16, or null when Xf is given
@@ -35,6 +40,14 @@ struct Args {
   void* C;
   const float* bias;     // per weight row, or null
   int M, N, K, ldx, ldw, ldc, accumulate;
+  // NORM_SCALED: X holds bfloat16(x * norm weight); ssq_in [M, ssq_parts] are partial sums of x^2
+  const float* ssq_in;
+  int ssq_parts;
+  // EMIT: beside C (float32, the residual rows) the kernel writes emit_x [M, N] = bfloat16(C * emit_w)
+  // and emit_ssq [M, ceil(N / 16)] = sums of C^2 over 16 columns, for the norm that reads C next
+  const float* emit_w;
+  bf16* emit_x;
+  float* emit_ssq;
   // EPI_CONV
   float* conv_state;     // [slots, taps-1, N] float32
   const float* conv_taps;  // [taps, N]
@@ -69,8 +82,9 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 // RG: groups of 16 weight rows per block; NT: groups of 8 tokens; UNROLL: 32-wide k slabs whose
 // weight loads are in flight together.  N is the number of output columns; for EPI_PLAIN weight
 // row = column, for the fused epilogues block b holds weight rows b*16*RG .. (interleaved parts).
-template <int WARPS, int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
+template <int WARPS, int RG, int NT, int UNROLL, int EPI, int NORM_MODE, typename TC, bool EMIT = false>
 __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
+  constexpr bool NORM = NORM_MODE == NORM_FUSED;   // the prologue that normalises float32 rows
   extern __shared__ float smem[];
   constexpr int RED_LD = NT * 8 + 1;
   float(*red)[RG * 16][RED_LD] = reinterpret_cast<float(*)[RG * 16][RED_LD]>(smem);
@@ -143,6 +157,16 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
   // NORM: the block normalises the M rows once into shared memory as bfloat16 (row stride padded
   // by 16 bytes so that the 8 rows a fragment load touches fall into different banks).
   const int xs_ld = K + 8;
+  if constexpr (NORM_MODE == NORM_SCALED) {
+    // one warp per row adds the row's partial sums in a fixed order; read after the barrier that
+    // follows the main loop
+    for (int m = warp; m < M; m += WARPS) {
+      float t = 0.f;
+      for (int p = lane; p < a.ssq_parts; p += 32) t += a.ssq_in[(size_t)m * a.ssq_parts + p];
+      t = warp_sum(t);
+      if (lane == 0) row_scale[m] = 1.0f / sqrtf(t / (float)K + a.eps);
+    }
+  }
   if constexpr (NORM) {
     float* part = row_scale + NT * 8;  // [NT * 8][WARPS] partial sums of squares
     constexpr int TH = WARPS * 32;
@@ -319,7 +343,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) v += red[w][row][m];
-    if (NORM && norm_one_pass) v *= row_scale[m];   // the rows were staged without their scale
+    if ((NORM && norm_one_pass) || NORM_MODE == NORM_SCALED) v *= row_scale[m];   // the rows came without their scale
     return v;
   };
 
@@ -328,12 +352,25 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
     for (int idx = threadIdx.x; idx < RG * 16 * NT * 8; idx += WARPS * 32) {
       const int m = idx / (RG * 16), nl = idx % (RG * 16);
       const int n = n0 + nl;
-      if (m >= M || n >= N) continue;
-      float v = total(nl, m);
-      if (a.bias) v += a.bias[n];
-      TC* dst = C + (size_t)m * a.ldc + n;
-      if (a.accumulate) v += to_f32(*dst);
-      *dst = from_f32<TC>(v);
+      const bool in = m < M && n < N;
+      if (!EMIT && !in) continue;
+      float v = 0.f;
+      if (in) {
+        v = total(nl, m);
+        if (a.bias) v += a.bias[n];
+        TC* dst = C + (size_t)m * a.ldc + n;
+        if (a.accumulate) v += to_f32(*dst);
+        *dst = from_f32<TC>(v);
+      }
+      if constexpr (EMIT) {
+        // whole warps run this loop (its bound is a multiple of 32); 16 adjacent lanes hold 16
+        // adjacent columns of one row
+        if (in) a.emit_x[(size_t)m * N + n] = __float2bfloat16_rn(v * a.emit_w[n]);
+        float sq = v * v;
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        if ((nl & 15) == 0 && m < M && n < N) a.emit_ssq[(size_t)m * ((N + 15) / 16) + n / 16] = sq;
+      }
     }
   } else if constexpr (EPI == EPI_SWIGLU) {
     bf16* C = reinterpret_cast<bf16*>(a.C);
@@ -393,9 +430,10 @@ size_t smem_bytes(bool norm, int K) {
   return sizeof(float) * floats + (norm ? sizeof(bf16) * (size_t)NT * 8 * (K + 8) : 0);
 }
 
-template <int WARPS, int RG, int NT, int UNROLL, int EPI, bool NORM, typename TC>
+template <int WARPS, int RG, int NT, int UNROLL, int EPI, int NORM_MODE, typename TC, bool EMIT = false>
 int launch(const Args& a, cudaStream_t stream) {
-  auto kern = skinny_kernel<WARPS, RG, NT, UNROLL, EPI, NORM, TC>;
+  auto kern = skinny_kernel<WARPS, RG, NT, UNROLL, EPI, NORM_MODE, TC, EMIT>;
+  constexpr bool NORM = NORM_MODE == NORM_FUSED;
   const size_t smem = smem_bytes<WARPS, RG, NT>(NORM, a.K);
   if (smem > 200 * 1024) return ZK_EINVAL;
   if (smem > 48 * 1024) {
@@ -410,36 +448,56 @@ int launch(const Args& a, cudaStream_t stream) {
 // Shapes are chosen so that a block streams enough weights to pay for its start-up and so that an
 // SM has some 64 KB of loads in flight: 16 warps where N gives few blocks, 32 rows per block
 // where N gives many.
-template <bool NORM, typename TC>
+template <int NORM_MODE, typename TC>
 int dispatch_plain(const Args& a, cudaStream_t stream) {
   const bool few = a.N <= 16 * 148 * 2;    // at most two 16-row blocks per SM: make each block wider in K
   const bool many = a.N >= 16 * 148 * 6;   // many blocks: 32 rows each
   if (a.M <= 8) {
-    if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
-    if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
-    return launch<8, 1, 1, 4, EPI_PLAIN, NORM, TC>(a, stream);
+    if constexpr (NORM_MODE == NORM_NONE && std::is_same<TC, float>::value) {
+      if (a.emit_x) {
+        if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
+        if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
+        return launch<8, 1, 1, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
+      }
+    }
+    if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
+    if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
+    return launch<8, 1, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
   }
   if (a.M <= 16) {
-    if (few) return launch<16, 1, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
-    if (many) return launch<8, 2, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
-    return launch<8, 1, 2, 4, EPI_PLAIN, NORM, TC>(a, stream);
+    if (few) return launch<16, 1, 2, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
+    if (many) return launch<8, 2, 2, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
+    return launch<8, 1, 2, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
   }
-  if constexpr (NORM) {
+  if constexpr (NORM_MODE != NORM_NONE) {
     return ZK_EINVAL;
   } else {
     // the split of K over the warps must not depend on M, or a row's bits would depend on its batch
-    if (a.M <= 32) return few ? launch<16, 1, 4, 2, EPI_PLAIN, false, TC>(a, stream)
-                              : launch<8, 2, 4, 2, EPI_PLAIN, false, TC>(a, stream);
-    return few ? launch<16, 1, 8, 1, EPI_PLAIN, false, TC>(a, stream) : launch<8, 1, 8, 2, EPI_PLAIN, false, TC>(a, stream);
+    if (a.M <= 32) return few ? launch<16, 1, 4, 2, EPI_PLAIN, NORM_NONE, TC>(a, stream)
+                              : launch<8, 2, 4, 2, EPI_PLAIN, NORM_NONE, TC>(a, stream);
+    return few ? launch<16, 1, 8, 1, EPI_PLAIN, NORM_NONE, TC>(a, stream) : launch<8, 1, 8, 2, EPI_PLAIN, NORM_NONE, TC>(a, stream);
   }
+}
+
+template <typename TC>
+int dispatch_plain_any(const Args& a, cudaStream_t stream) {
+  if (a.Xf) return dispatch_plain<NORM_FUSED, TC>(a, stream);
+  if (a.ssq_in) return dispatch_plain<NORM_SCALED, TC>(a, stream);
+  return dispatch_plain<NORM_NONE, TC>(a, stream);
+}
+
+template <int RG, int EPI, int NORM_MODE>
+int dispatch_fused_mode(const Args& a, cudaStream_t stream) {
+  if (a.M <= 8) return launch<8, RG, 1, 4, EPI, NORM_MODE, bf16>(a, stream);
+  if (a.M <= 16) return launch<8, RG, 2, 2, EPI, NORM_MODE, bf16>(a, stream);
+  return ZK_EINVAL;
 }
 
 template <int RG, int EPI>
 int dispatch_fused(const Args& a, cudaStream_t stream) {
-  const bool norm = a.Xf != nullptr;
-  if (a.M <= 8) return norm ? launch<8, RG, 1, 4, EPI, true, bf16>(a, stream) : launch<8, RG, 1, 4, EPI, false, bf16>(a, stream);
-  if (a.M <= 16) return norm ? launch<8, RG, 2, 2, EPI, true, bf16>(a, stream) : launch<8, RG, 2, 2, EPI, false, bf16>(a, stream);
-  return ZK_EINVAL;
+  if (a.Xf) return dispatch_fused_mode<RG, EPI, NORM_FUSED>(a, stream);
+  if (a.ssq_in) return dispatch_fused_mode<RG, EPI, NORM_SCALED>(a, stream);
+  return dispatch_fused_mode<RG, EPI, NORM_NONE>(a, stream);
 }
 
 int check_common(const Args& a, int max_m) {
@@ -449,6 +507,7 @@ int check_common(const Args& a, int max_m) {
     if (a.ldx % 4 || (uintptr_t)a.Xf % 16 || (uintptr_t)a.norm_w % 16 || !a.norm_w) return ZK_EINVAL;
   } else {
     if (!a.X || a.ldx % 8 || (uintptr_t)a.X % 16) return ZK_EINVAL;
+    if (a.ssq_in && (a.ssq_parts <= 0 || a.M > 16)) return ZK_EINVAL;
   }
   return 0;
 }
@@ -462,27 +521,36 @@ int zk_gemm_skinny_fused_max_m() { return 16; }
 
 // X [M, K] bfloat16 (or Xf [M, K] float32 + norm_w [K], eps: RMSNorm fused, M <= 16), W [N, K]
 // bfloat16 with K % 8 == 0 and 16-byte aligned rows; C [M, N] bfloat16 or float32.
+// ssq_in [M, ssq_parts] (or null): X is bfloat16(x * norm weight) and the sums are scaled by
+// 1 / sqrt(sum(ssq_in[m]) / K + eps) (M <= 16).  emit_x (or null; M <= 8, float32 C, no fused norm):
+// also writes emit_x [M, N] = bfloat16(C * emit_w) and emit_ssq [M, ceil(N / 16)] for the next norm.
 int zk_gemm_skinny(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* C,
                    const float* bias, int M, int N, int K, int ldx, int ldw, int ldc, int out_dtype, int accumulate,
+                   const float* ssq_in, int ssq_parts, const float* emit_w, void* emit_x, float* emit_ssq,
                    cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   Args a{};
   a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = C; a.bias = bias;
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldc; a.accumulate = accumulate;
+  a.ssq_in = Xf ? nullptr : ssq_in; a.ssq_parts = ssq_parts;
+  a.emit_w = emit_w; a.emit_x = (bf16*)emit_x; a.emit_ssq = emit_ssq;
   if (ldc < N || check_common(a, Xf ? 16 : 64)) return ZK_EINVAL;
-  if (out_dtype == ZK_F32) return Xf ? dispatch_plain<true, float>(a, stream) : dispatch_plain<false, float>(a, stream);
-  if (out_dtype == ZK_BF16) return Xf ? dispatch_plain<true, bf16>(a, stream) : dispatch_plain<false, bf16>(a, stream);
+  if (emit_x && (!emit_w || !emit_ssq || M > 8 || Xf || out_dtype != ZK_F32)) return ZK_EINVAL;
+  if (out_dtype == ZK_F32) return dispatch_plain_any<float>(a, stream);
+  if (out_dtype == ZK_BF16) return dispatch_plain_any<bf16>(a, stream);
   return ZK_EINVAL;
 }
 
 // h[M, F] = silu(x W_gate^T) * (x W_up^T); W [2F, K] holds groups of 16 gate rows followed by their
 // 16 up rows (F a multiple of 16); M <= 16.
 int zk_gemm_skinny_swiglu(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* H,
-                          int M, int F, int K, int ldx, int ldw, int ldh, cudaStream_t stream) {
+                          int M, int F, int K, int ldx, int ldw, int ldh, const float* ssq_in, int ssq_parts,
+                          cudaStream_t stream) {
   if (M <= 0 || F <= 0) return 0;
   Args a{};
   a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = H;
   a.M = M; a.N = F; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldh;
+  a.ssq_in = Xf ? nullptr : ssq_in; a.ssq_parts = ssq_parts;
   if (ldh < F || F % 16 || check_common(a, 16)) return ZK_EINVAL;
   return dispatch_fused<2, EPI_SWIGLU>(a, stream);
 }
@@ -494,13 +562,14 @@ int zk_gemm_skinny_swiglu(const void* X, const float* Xf, const float* norm_w, f
 int zk_gemm_skinny_conv(const void* X, const float* Xf, const float* norm_w, float eps, const void* W,
                         const float* in_bias, float* state, const float* taps_w, const float* conv_bias,
                         const int* seq_slot, void* Y, int M, int D, int K, int taps, int ldx, int ldw, int ldy,
-                        long long state_stride, cudaStream_t stream) {
+                        long long state_stride, const float* ssq_in, int ssq_parts, cudaStream_t stream) {
   if (M <= 0 || D <= 0) return 0;
   Args a{};
   a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = Y; a.bias = in_bias;
   a.M = M; a.N = D; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldy;
   a.conv_state = state; a.conv_taps = taps_w; a.conv_bias = conv_bias; a.seq_slot = seq_slot; a.taps = taps;
   a.state_stride = state_stride;
+  a.ssq_in = Xf ? nullptr : ssq_in; a.ssq_parts = ssq_parts;
   if (ldy < D || D % 16 || taps < 2 || !state || !taps_w || !seq_slot || check_common(a, 16)) return ZK_EINVAL;
   return dispatch_fused<3, EPI_CONV>(a, stream);
 }

@@ -32,9 +32,9 @@ _SIGNATURES = {
         "zk_gemm_simt": "ppppiiiiiiiiip",
     },
     "gemm_skinny": {
-        "zk_gemm_skinny": "pppfpppiiiiiiiip",
-        "zk_gemm_skinny_swiglu": "pppfppiiiiiip",
-        "zk_gemm_skinny_conv": "pppfppppppp" + "iiiiiiilp",
+        "zk_gemm_skinny": "pppfpppiiiiiiii" + "pippp" + "p",
+        "zk_gemm_skinny_swiglu": "pppfppiiiiii" + "pi" + "p",
+        "zk_gemm_skinny_conv": "pppfppppppp" + "iiiiiiil" + "pi" + "p",
         "zk_gemm_skinny_max_m": "",
         "zk_gemm_skinny_fused_max_m": "",
     },
@@ -335,16 +335,48 @@ class NormInput:
         return self.x.shape
 
 
+class ScaledInput:
+    """Rows of the residual stream as the kernel that summed them left them for the next RMSNorm:
+    xw [M, K] = bfloat16(x * norm weight) and ssq [M, parts] float32, partial sums of x^2 whose
+    sum over `parts` is the row's.  The skinny kernels take it in place of a bfloat16 input and
+    scale their sums by 1 / sqrt(sum(ssq) / K + eps)."""
+
+    def __init__(self, xw: torch.Tensor, ssq: torch.Tensor, eps: float):
+        _need(xw, "xw", torch.bfloat16, (None, None))
+        _need(ssq, "ssq", torch.float32, (xw.shape[0], None))
+        self.xw, self.ssq, self.eps = xw, ssq, float(eps)
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+
+class NormEmit:
+    """What an accumulating contraction into the residual rows writes for the norm that reads them
+    next: `weight` [N] of that norm; after the call `xw` [M, N] and `ssq` [M, ceil(N / 16)]."""
+
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight
+        self.xw: Optional[torch.Tensor] = None
+        self.ssq: Optional[torch.Tensor] = None
+
+
+GEMM_SKINNY_EMIT_MAX_M = 8
+
+
 def _skinny_input(a):
-    """(X pointer, Xf pointer, norm weight pointer, eps, M, K, ldx) of a bfloat16 tensor or a NormInput."""
+    """(X pointer, Xf pointer, norm weight pointer, eps, M, K, ldx, ssq pointer, ssq parts) of a
+    bfloat16 tensor, a NormInput or a ScaledInput."""
     if isinstance(a, NormInput):
-        return None, _ptr(a.x), _ptr(a.weight), a.eps, a.x.shape[0], a.x.shape[1], a.x.stride(0)
-    return _ptr(a), None, None, 0.0, a.shape[0], a.shape[1], a.stride(0)
+        return None, _ptr(a.x), _ptr(a.weight), a.eps, a.x.shape[0], a.x.shape[1], a.x.stride(0), None, 0
+    if isinstance(a, ScaledInput):
+        return _ptr(a.xw), None, None, a.eps, a.xw.shape[0], a.xw.shape[1], a.xw.stride(0), _ptr(a.ssq), a.ssq.shape[1]
+    return _ptr(a), None, None, 0.0, a.shape[0], a.shape[1], a.stride(0), None, 0
 
 
 def gemm_skinny_takes(a, w: torch.Tensor) -> bool:
     """Whether the skinny kernels take this contraction: bfloat16 weights, few rows, 16-byte
-    aligned rows.  `a` is a bfloat16 tensor [M <= 64, K] or a NormInput [M <= 16, K]."""
+    aligned rows.  `a` is a bfloat16 tensor [M <= 64, K], a NormInput or a ScaledInput [M <= 16, K]."""
     if not (w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.stride(0) % 8 == 0
             and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0):
         return False
@@ -352,6 +384,10 @@ def gemm_skinny_takes(a, w: torch.Tensor) -> bool:
         x = a.x
         return (x.shape[0] <= gemm_skinny_fused_max_m() and x.shape[1] == w.shape[1] and x.stride(1) == 1
                 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and a.weight.data_ptr() % 16 == 0)
+    if isinstance(a, ScaledInput):
+        if a.xw.shape[0] > gemm_skinny_fused_max_m() or not a.ssq.is_contiguous():
+            return False
+        a = a.xw
     return (a.dtype == torch.bfloat16 and a.dim() == 2 and a.shape[0] <= gemm_skinny_max_m()
             and a.shape[1] == w.shape[1] and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0)
 
@@ -361,14 +397,23 @@ def gemm_skinny_fused_takes(a, w: torch.Tensor) -> bool:
     return gemm_skinny_takes(a, w) and a.shape[0] <= gemm_skinny_fused_max_m()
 
 
+def gemm_skinny_emits(a, out: Optional[torch.Tensor]) -> bool:
+    """Whether `gemm_skinny` can write a NormEmit beside `out` for this input."""
+    return (isinstance(a, torch.Tensor) and a.shape[0] <= GEMM_SKINNY_EMIT_MAX_M and out is not None
+            and out.dtype == torch.float32 and out.is_contiguous())
+
+
 def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
-                accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                accumulate: bool = False, bias: Optional[torch.Tensor] = None,
+                emit: Optional[NormEmit] = None) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) for a [M <= 64, K] on the tensor cores, every weight read once.
-    With a NormInput the RMSNorm of the rows is applied inside the kernel."""
+    With a NormInput the RMSNorm of the rows is applied inside the kernel; with a ScaledInput the
+    sums are scaled by the rows' 1/rms.  `emit` (see `gemm_skinny_emits`) is filled for the norm
+    that reads `out` next."""
     if not gemm_skinny_takes(a, w):
         raise KernelError(f"gemm_skinny: a {tuple(a.shape)} / w {tuple(w.shape)} need few rows, "
                           "K a multiple of 8 and 16-byte aligned rows")
-    X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
+    X, Xf, nw, eps, M, K, ldx, ssq, ssq_parts = _skinny_input(a)
     N = w.shape[0]
     if out is None:
         if accumulate:
@@ -377,9 +422,18 @@ def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtyp
     _need(out, "out", (torch.float32, torch.bfloat16), (M, N))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
+    if emit is not None:
+        if not gemm_skinny_emits(a, out):
+            raise KernelError("gemm_skinny: the norm's inputs are written for at most 8 bfloat16 rows "
+                              "summed into contiguous float32 rows")
+        _need(emit.weight, "norm weight", torch.float32, (N,))
+        emit.xw = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+        emit.ssq = torch.empty((M, -(-N // 16)), dtype=torch.float32, device=w.device)
     _check(_fn("gemm_skinny", "zk_gemm_skinny")(X, Xf, nw, eps, _ptr(w), _ptr(out), _ptr(bias), M, N, K, ldx,
                                                 w.stride(0), out.stride(0), dtype_code(out.dtype),
-                                                1 if accumulate else 0, _stream()), "gemm_skinny")
+                                                1 if accumulate else 0, ssq, ssq_parts,
+                                                _ptr(emit.weight) if emit else None, _ptr(emit.xw) if emit else None,
+                                                _ptr(emit.ssq) if emit else None, _stream()), "gemm_skinny")
     return out
 
 
@@ -388,11 +442,12 @@ def gemm_skinny_swiglu(a, w_gate_up: torch.Tensor) -> torch.Tensor:
     rows followed by their 16 up rows."""
     if not gemm_skinny_fused_takes(a, w_gate_up) or w_gate_up.shape[0] % 32:
         raise KernelError("gemm_skinny_swiglu: at most 16 rows, K a multiple of 8, 16-byte aligned rows")
-    X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
+    X, Xf, nw, eps, M, K, ldx, ssq, ssq_parts = _skinny_input(a)
     F = w_gate_up.shape[0] // 2
     h = torch.empty((M, F), dtype=torch.bfloat16, device=w_gate_up.device)
     _check(_fn("gemm_skinny", "zk_gemm_skinny_swiglu")(X, Xf, nw, eps, _ptr(w_gate_up), _ptr(h), M, F, K, ldx,
-                                                       w_gate_up.stride(0), h.stride(0), _stream()),
+                                                       w_gate_up.stride(0), h.stride(0), ssq, ssq_parts,
+                                                       _stream()),
            "gemm_skinny_swiglu")
     return h
 
@@ -404,7 +459,7 @@ def gemm_skinny_conv(a, w_in: torch.Tensor, in_bias, state: torch.Tensor, taps: 
     in_bias [3D] hold groups of 16 B rows, 16 C rows, 16 X rows."""
     if not gemm_skinny_fused_takes(a, w_in) or w_in.shape[0] % 48:
         raise KernelError("gemm_skinny_conv: at most 16 rows, K a multiple of 8, 16-byte aligned rows")
-    X, Xf, nw, eps, M, K, ldx = _skinny_input(a)
+    X, Xf, nw, eps, M, K, ldx, ssq, ssq_parts = _skinny_input(a)
     D = w_in.shape[0] // 3
     _need(taps, "conv weight", torch.float32, (None, D))
     n_taps = taps.shape[0]
@@ -417,7 +472,8 @@ def gemm_skinny_conv(a, w_in: torch.Tensor, in_bias, state: torch.Tensor, taps: 
     y = torch.empty((M, D), dtype=torch.bfloat16, device=w_in.device)
     _check(_fn("gemm_skinny", "zk_gemm_skinny_conv")(X, Xf, nw, eps, _ptr(w_in), _ptr(in_bias), _ptr(state), _ptr(taps),
                                                      _ptr(conv_bias), _ptr(seq_slot), _ptr(y), M, D, K, n_taps, ldx,
-                                                     w_in.stride(0), y.stride(0), state.stride(0), _stream()),
+                                                     w_in.stride(0), y.stride(0), state.stride(0), ssq, ssq_parts,
+                                                     _stream()),
            "gemm_skinny_conv")
     return y
 

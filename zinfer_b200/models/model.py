@@ -83,10 +83,15 @@ class Model:
         (written into `out` if given), or None when none is wanted.  Only wanted rows meet the
         final norm and the head (src/model.zig:2482-2490)."""
         x = self.embedding.forward(ctx, ctx.tokens)
-        for call_ctx in calls:
-            self.layers[call_ctx.layer].forward(ctx, call_ctx, x)
+        carried = None      # what a block's last contraction prepared for the norm that reads x next
+        for i, call_ctx in enumerate(calls):
+            if i + 1 < len(calls):
+                next_norm = self.layers[calls[i + 1].layer].entry_norm()
+            else:
+                next_norm = self.final_norm if want_all else None
+            carried = self.layers[call_ctx.layer].forward_chained(ctx, call_ctx, x, carried, next_norm)
         if want_all:
-            return self.head.forward(ctx, normed_for(self.head, self.final_norm, ctx, x), out=out)
+            return self.head.forward(ctx, normed_for(self.head, self.final_norm, ctx, x, carried), out=out)
         if want_rows is None or want_rows.numel() == 0:
             return None
         xn = self.final_norm.forward(ctx, x, rows=want_rows)

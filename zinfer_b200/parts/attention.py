@@ -135,6 +135,7 @@ class GqaAttention(Mixer):
         return key_chunks(n_seqs, self.n_kv, longest, self._sm_count, self.split_keys)
 
     takes_pending_norm = True
+    sums_through_linear = True
 
     def forward(self, ctx, call, xn, out, accumulate):
         kv = call.kv

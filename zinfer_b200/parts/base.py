@@ -13,6 +13,8 @@ Part            weight_specs() -> [WeightSpec]; load(weights: dict name -> tenso
 Norm            forward(ctx, x_f32, rows=None) -> tensor in the run dtype
                 pending(ctx, x_f32) -> object | None   optional: the norm not yet applied, for a
                                                        consumer that can apply it itself
+                ahead(ctx, x_f32) -> object | None     optional: a stand-in for x as the `out` of the
+                                                       contraction that sums into x before this norm
 PositionEncoding  rotary() -> RotaryParams | None (lets the mixer fuse it), or
                   apply(ctx, q, k) -> None to rotate / shift in place on its own
 Mixer           kv_request() -> KVRequest | None      growing cache it needs
@@ -23,6 +25,12 @@ Mixer           kv_request() -> KVRequest | None      growing cache it needs
                 launch_key(n_seqs, longest)           what a recorded single-token step bakes in
 FeedForward     forward(ctx, xn, out, accumulate)
 Block           forward(ctx, call, x)  updates the float32 residual stream x in place
+                entry_norm() / forward_chained(...)   optional: lets the kernel that writes x last in
+                                                       one block prepare the first norm of the next
+
+Optional flags of a mixer or feed-forward, read by the block (parts.block):
+takes_pending_norm     its input may be the norm's pending form
+sums_through_linear    `out` is used only as `out=` of its last `linear` call and may be a ResidualSink
 """
 from __future__ import annotations
 
@@ -105,7 +113,8 @@ class Norm(Part):
     def pending(self, ctx, x: torch.Tensor):
         """The norm of all rows of `x` as an object that a consumer with `takes_pending_norm`
         resolves itself (parts.linear.NormedRows), or None if this norm has no such form; the
-        caller then uses `forward`."""
+        caller then uses `forward`.  A norm that also has `ahead(ctx, x)` takes what that returned
+        as a third argument."""
         return None
 
 
@@ -154,6 +163,18 @@ class Block(Part):
 
     def forward(self, ctx, call, x: torch.Tensor) -> None:
         raise NotImplementedError
+
+    def entry_norm(self) -> Optional[Norm]:
+        """The norm this block applies to `x` before anything else, if the block before may
+        prepare it (see forward_chained); None = nothing to prepare."""
+        return None
+
+    def forward_chained(self, ctx, call, x: torch.Tensor, entry=None, next_norm: Optional[Norm] = None):
+        """As `forward`.  `entry`: what the block before returned, prepared for this block's
+        entry_norm().  `next_norm`: the norm that reads `x` after this block.  Returns what this
+        block's last contraction prepared for `next_norm` (to be handed on as `entry`), or None."""
+        self.forward(ctx, call, x)
+        return None
 
 
 # ------------------------------------------------------------------------------- registries

@@ -14,6 +14,7 @@ from .linear_bf16 import TC_SWAPPED_MIN_ROWS, swapped_splits
 
 class SwiGLU(FeedForward):
     takes_pending_norm = True
+    sums_through_linear = True
 
     def __init__(self, hidden: int, ffn_dim: int, gate_name: str, up_name: str, down_name: str):
         self.hidden, self.ffn_dim = hidden, ffn_dim

@@ -8,6 +8,11 @@ kernel when the shape allows one and the same FMA kernel otherwise.
 `a` may be a `NormedRows`: rows of the residual stream whose RMSNorm is still to be applied.
 A kernel that can normalise its input itself takes it as it is; for any other kernel the norm
 runs first, once, however many contractions read it.
+
+`out` may be a `ResidualSink`: the residual rows together with the norm that reads them next.
+A kernel that can then writes, beside the sum, what that norm needs (the rows times the norm's
+weight in bfloat16 and partial sums of their squares), and the contraction behind the norm
+scales its own sums by the rows' 1/rms: the norm costs neither a launch nor a pass over the rows.
 """
 from __future__ import annotations
 
@@ -21,8 +26,10 @@ from .. import kernels
 class NormedRows:
     """RMSNorm(x) * weight that is computed when somebody needs it as a tensor."""
 
-    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: torch.dtype):
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: torch.dtype,
+                 scaled: Optional["kernels.NormEmit"] = None):
         self.x, self.weight, self.eps, self.dtype = x, weight, eps, dtype
+        self.scaled = scaled          # what the kernel that summed x wrote for this norm, if it did
         self._tensor: Optional[torch.Tensor] = None
 
     @property
@@ -36,6 +43,17 @@ class NormedRows:
 
     def kernel_input(self) -> "kernels.NormInput":
         return kernels.NormInput(self.x, self.weight, self.eps)
+
+
+class ResidualSink:
+    """The float32 residual rows as the target of an accumulating contraction (`linear(...,
+    out=sink, accumulate=True)`), with the weight of the RMSNorm that reads them next.  `emit`
+    is set once a kernel has written that norm's inputs beside the sum; it stays None when the
+    kernel that ran cannot, and the norm then works from the rows as ever."""
+
+    def __init__(self, rows: torch.Tensor, norm_weight: torch.Tensor):
+        self.rows, self.norm_weight = rows, norm_weight
+        self.emit: Optional["kernels.NormEmit"] = None
 
 
 FUSION_GROUP = 16     # rows per part and group in the interleaved weight layouts of the fused kernels
@@ -75,6 +93,10 @@ def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_
         if a.dtype != torch.bfloat16:
             return None
         if a._tensor is None:
+            if a.scaled is not None:
+                si = kernels.ScaledInput(a.scaled.xw, a.scaled.ssq, a.eps)
+                if takes(si, w):
+                    return si
             ki = a.kernel_input()
             n_blocks = blocks if blocks is not None else -(-w.shape[0] // 16)
             worth = n_blocks <= NORM_FUSION_MAX_BLOCKS or a.shape[0] <= NORM_FUSION_ANY_BLOCKS_ROWS
@@ -84,13 +106,17 @@ def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_
     return a if takes(a, w) else None
 
 
-def linear(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+def linear(a: Union[torch.Tensor, NormedRows], w: torch.Tensor,
+           out: Union[torch.Tensor, ResidualSink, None] = None, out_dtype=None,
            accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a [M, K] and w [N, K] in the run dtype; result [M, N] in `out_dtype` (default: run dtype),
     or added into `out` when `accumulate`."""
+    sink = None
+    if isinstance(out, ResidualSink):
+        sink, out = out, out.rows
     if w.dtype == torch.bfloat16:
         from . import linear_bf16
-        y = linear_bf16.try_linear(a, w, out, out_dtype, accumulate, bias)
+        y = linear_bf16.try_linear(a, w, out, out_dtype, accumulate, bias, sink)
         if y is not None:
             return y
     return kernels.gemm_simt(as_tensor(a), w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)

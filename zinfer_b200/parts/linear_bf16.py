@@ -24,7 +24,7 @@ def swapped_splits(n_weight_rows: int) -> int:
     return 1 << (want.bit_length() - 1)
 
 
-def try_linear(a, w, out, out_dtype, accumulate, bias):
+def try_linear(a, w, out, out_dtype, accumulate, bias, sink=None):
     from .linear import as_tensor, fused_input
 
     if TC_SWAPPED_MIN_ROWS <= a.shape[0] <= kernels.gemm_skinny_max_m():
@@ -34,7 +34,13 @@ def try_linear(a, w, out, out_dtype, accumulate, bias):
                                    splits=swapped_splits(w.shape[0]))
     x = fused_input(a, w)
     if x is not None:
-        return kernels.gemm_skinny(x, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)
+        emit = None
+        if sink is not None and kernels.gemm_skinny_emits(x, out):
+            emit = kernels.NormEmit(sink.norm_weight)
+        y = kernels.gemm_skinny(x, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias, emit=emit)
+        if emit is not None:
+            sink.emit = emit
+        return y
     a = as_tensor(a)
     if kernels.gemm_tc_takes(a, w, out):
         return kernels.gemm_tc(a, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)

@@ -8,7 +8,7 @@ import torch
 
 from .. import kernels
 from .base import NORMS, Norm, WeightSpec
-from .linear import NormedRows
+from .linear import NormedRows, ResidualSink
 
 
 class RMSNorm(Norm):
@@ -25,9 +25,21 @@ class RMSNorm(Norm):
     def forward(self, ctx, x, rows=None):
         return kernels.rmsnorm(x, self.weight, self.eps, ctx.dtype, rows)
 
-    def pending(self, ctx, x):
-        """All rows, not yet normalised: `linear` and the fused kernels resolve a `NormedRows`."""
-        return NormedRows(x, self.weight, self.eps, ctx.dtype)
+    def pending(self, ctx, x, prepared=None):
+        """All rows, not yet normalised: `linear` and the fused kernels resolve a `NormedRows`.
+        `prepared` is what `ahead` returned for these rows, after the contraction that got it ran."""
+        emit = None
+        if (isinstance(prepared, ResidualSink) and prepared.emit is not None and prepared.rows is x
+                and prepared.norm_weight is self.weight):
+            emit = prepared.emit
+        return NormedRows(x, self.weight, self.eps, ctx.dtype, scaled=emit)
+
+    def ahead(self, ctx, x):
+        """For the few rows of a single-token step in bfloat16: the contraction that sums into `x`
+        can write this norm's inputs along (see `linear`)."""
+        if ctx.dtype != torch.bfloat16 or x.shape[0] > kernels.GEMM_SKINNY_EMIT_MAX_M:
+            return None
+        return ResidualSink(x, self.weight)
 
 
 NORMS.register("rmsnorm", RMSNorm)

@@ -65,6 +65,7 @@ class ShortConv(Mixer):
         return StateRequest((self.K - 1, self.hidden), torch.float32)
 
     takes_pending_norm = True
+    sums_through_linear = True
 
     def forward(self, ctx, call, xn, out, accumulate):
         state = call.state
