@@ -281,13 +281,15 @@ def test_gemm_skinny_swiglu(k, M, F, K, norm):
 @pytest.mark.parametrize("M,F,K", [(65, 64, 64), (300, 8192, 2048), (130, 208, 520), (64, 8192, 2048), (17, 208, 520),
                                    (40, 64, 64), (1, 32, 64), (700, 8192, 256), (2100, 2304, 96)])
 def test_gemm_tc_with_swiglu_epilogue(k, M, F, K):
-    """Normal mode (more than 64 rows) and swapped mode (the weights on the 128-row side, K whole)."""
+    """Normal mode (more than 64 rows) and swapped mode (the weights on the 128-row side; K whole, and
+    cut into 2, 4 and 8 parts over a cluster)."""
     a = rnd((M, K), 1, torch.bfloat16).cuda()
     halves = rnd((2 * F, K), 3, torch.bfloat16, 0.3).cuda()
     g, u = a.double() @ halves[:F].double().T, a.double() @ halves[F:].double().T
-    h = k.gemm_tc(a, interleaved([halves[:F], halves[F:]]), swiglu=True)
-    assert h.shape == (M, F)
-    close(h, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "tcgen05 contraction with SwiGLU epilogue")
+    for splits in (1, 2, 4, 8) if M <= 64 else (1,):
+        h = k.gemm_tc(a, interleaved([halves[:F], halves[F:]]), swiglu=True, splits=splits)
+        assert h.shape == (M, F)
+        close(h, g / (1 + torch.exp(-g)) * u, torch.bfloat16, f"tcgen05 contraction with SwiGLU epilogue, K in {splits}")
     assert k.status_word("cuda").item() == 0
 
 

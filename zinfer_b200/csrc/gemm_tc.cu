@@ -314,29 +314,43 @@ __global__ void __launch_bounds__(THREADS)
         const unsigned rank = cluster_rank();
         if (n < p.N) {
           const float b = p.bias ? p.bias[n] : 0.f;
-          // four tokens at a time: their remote partials (up to 8 blocks in a cluster) and old
-          // values are all requested before the first sum, so a thread waits for them once, not
-          // once per token
-          for (int t0 = (int)rank; t0 < p.M; t0 += 4 * p.splits) {
-            float pv[4][8], old[4];
+          // The remote partials and old values of 32 / splits tokens (32 loads from the cluster's
+          // shared memory and up to 16 from global memory) are all requested before the first sum,
+          // so a thread waits for them once, not once per token: with four tokens at a time the
+          // loop took longer than the contraction when K was split in two.
+          auto reduce = [&](auto splits_c) {
+            constexpr int SP = decltype(splits_c)::value, TOK = 32 / SP;
+            for (int t0 = (int)rank; t0 < p.M; t0 += TOK * SP) {
+              float pv[TOK][SP], old[TOK];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int t = t0 + i * p.splits;
+              for (int i = 0; i < TOK; ++i) {
+                const int t = t0 + i * SP;
 #pragma unroll
-              for (int z = 0; z < 8; ++z)
-                pv[i][z] = (t < p.M && z < p.splits) ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
-              old[i] = (t < p.M && p.accumulate) ? to_f32(C[(size_t)t * p.ldc + n]) : 0.f;
+                for (int z = 0; z < SP; ++z)
+                  pv[i][z] = t < p.M ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
+                old[i] = (t < p.M && p.accumulate) ? to_f32(C[(size_t)t * p.ldc + n]) : 0.f;
+              }
+#pragma unroll
+              for (int i = 0; i < TOK; ++i) {
+                const int t = t0 + i * SP;
+                if (t >= p.M) break;
+                float acc = b;
+#pragma unroll
+                for (int z = 0; z < SP; ++z) acc += pv[i][z];
+                if (p.swiglu) {
+                  // as in the unsplit epilogue: a warp's rows are 16 gate rows and their 16 up rows
+                  const float up = __shfl_down_sync(0xffffffffu, acc, 16);
+                  if ((lane & 16) == 0)
+                    C[(size_t)t * p.ldc + (n >> 5) * 16 + (n & 15)] = from_f32<TC>(acc / (1.0f + expf(-acc)) * up);
+                } else {
+                  C[(size_t)t * p.ldc + n] = from_f32<TC>(acc + old[i]);
+                }
+              }
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int t = t0 + i * p.splits;
-              if (t >= p.M) break;
-              float acc = b;
-#pragma unroll
-              for (int z = 0; z < 8; ++z) acc += pv[i][z];
-              C[(size_t)t * p.ldc + n] = from_f32<TC>(acc + old[i]);
-            }
-          }
+          };
+          if (p.splits == 2) reduce(std::integral_constant<int, 2>());
+          else if (p.splits == 4) reduce(std::integral_constant<int, 4>());
+          else reduce(std::integral_constant<int, 8>());
         }
       }
       __syncwarp();
@@ -750,7 +764,7 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
                int out_dtype, int accumulate, int splits, int swiglu, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < (swiglu ? N / 2 : N) || !status) return ZK_EINVAL;
-  if (swiglu && (N % 32 || bias || accumulate || (M <= 64 && splits > 1))) return ZK_EINVAL;
+  if (swiglu && (N % 32 || bias || accumulate)) return ZK_EINVAL;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
   if (out_dtype != ZK_F32 && out_dtype != ZK_BF16) return ZK_EINVAL;
   Params p{};

@@ -281,15 +281,15 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     blocks with tcgen05.mma.cta_group::2 above 128 rows, TMA stores), else one 128 x 128 tile of
     tokens x weight rows per block.  Up to 64 rows: the weights take
     the 128-row side and K is cut into `splits` (1, 2, 4 or 8) parts, one per block of a cluster,
-    that are added in order.  With `swiglu` (not with split K) w holds groups of 16 gate rows and
+    that are added in order.  With `swiglu` w holds groups of 16 gate rows and
     their 16 up rows and the result is silu(gate) * up, [M, N/2]."""
     if not gemm_tc_takes(a, w, out):
         raise KernelError(f"gemm_tc: a {tuple(a.shape)} / w {tuple(w.shape)} need bfloat16, K a multiple of 8 and "
                           "16-byte aligned rows")
     M, K = a.shape
     N = w.shape[0]
-    if swiglu and ((M <= 64 and splits > 1) or N % 32 or accumulate or bias is not None):
-        raise KernelError("gemm_tc: the SwiGLU epilogue needs unsplit K, N a multiple of 32, no bias")
+    if swiglu and (N % 32 or accumulate or bias is not None):
+        raise KernelError("gemm_tc: the SwiGLU epilogue needs N a multiple of 32, no bias and no accumulation")
     n_out = N // 2 if swiglu else N
     if out is None:
         if accumulate:

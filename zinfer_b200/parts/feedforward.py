@@ -39,17 +39,16 @@ class SwiGLU(FeedForward):
         if self.interleave and w.dtype == torch.bfloat16:
             from . import linear_bf16
             rows_in = xn.shape[0]
-            tc_rows = (rows_in >= linear_bf16.TC_SWAPPED_MIN_ROWS and rows_in <= kernels.gemm_skinny_max_m()
-                       and swapped_splits(w.shape[0]) == 1)
+            tc_rows = linear_bf16.TC_SWAPPED_MIN_ROWS <= rows_in <= kernels.gemm_skinny_max_m()
             x = None if tc_rows else fused_input(xn, w, need_fused_rows=True, blocks=self.ffn_dim // 16)
             if x is not None:                       # few rows: gate, up and the activation in one kernel
                 h = kernels.gemm_skinny_swiglu(x, w)
             else:
                 x = as_tensor(xn)
                 rows = x.shape[0]
-                # prompt steps, and steps of 17..64 rows whose K is not split: activation in the epilogue
+                # prompt steps, and steps of 9..64 rows: activation in the epilogue
                 if (rows > kernels.gemm_skinny_max_m() or tc_rows) and kernels.gemm_tc_takes(x, w):
-                    h = kernels.gemm_tc(x, w, swiglu=True)
+                    h = kernels.gemm_tc(x, w, swiglu=True, splits=swapped_splits(w.shape[0], kernels.sm_count(w.device)) if tc_rows else 1)
         if h is None:
             h = kernels.silu_mul(linear(xn, w), self.interleave)
         linear(h, self.w_down, out=out, accumulate=accumulate)

@@ -10,18 +10,23 @@ from .. import kernels
 
 
 # Between 9 and 64 rows the tcgen05 kernel with the weights on its 128-row side beats the mma.sync
-# kernel (measured at 64 rows on the LFM2-1.2B shapes: 18 us against 44 us for N = 16384, 13 against
-# 22 for N = 6144, 9 against 12 for N = 2048, 14 against 38 for N = 2048 with K = 8192; a whole step
+# kernel (measured at 64 rows on the LFM2-1.2B shapes: 17 us against 44 us for N = 16384, 10 against
+# 22 for N = 6144, 7 against 12 for N = 2048, 12 against 38 for N = 2048 with K = 8192; a whole step
 # of 9 sequences 0.97 against 1.13 ms, of 16 sequences 1.15 against 1.31 ms); up to 8 rows the
-# mma.sync kernel is as fast or faster.  K is split over a cluster when the weight matrix alone
-# gives fewer 128-row tiles than there are SMs.
+# mma.sync kernel is as fast or faster.
 TC_SWAPPED_MIN_ROWS = 9
 
 
-def swapped_splits(n_weight_rows: int) -> int:
+def swapped_splits(n_weight_rows: int, sm_count: int) -> int:
+    """In how many parts K is cut (one per block of a cluster): the fewest that give every SM a block.
+    Measured at 64 rows, microseconds for 1 / 2 / 4 / 8 parts: N = 2048 (16 tiles of 128 weight rows)
+    13 / 9 / 7 / 7, with K = 8192 41 / 23 / 15 / 12; N = 3072 14 / 9 / 7.5 / 8; N = 6144 15 / 11 / 10 / 15;
+    N = 16384 18 / 17 / 21 / 34."""
     tiles = -(-n_weight_rows // 128)
-    want = max(1, min(8, 192 // tiles))
-    return 1 << (want.bit_length() - 1)
+    s = 1
+    while s < 8 and tiles * s < sm_count:
+        s *= 2
+    return s
 
 
 def try_linear(a, w, out, out_dtype, accumulate, bias, sink=None):
@@ -31,7 +36,7 @@ def try_linear(a, w, out, out_dtype, accumulate, bias, sink=None):
         t = as_tensor(a)
         if kernels.gemm_tc_takes(t, w, out):
             return kernels.gemm_tc(t, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias,
-                                   splits=swapped_splits(w.shape[0]))
+                                   splits=swapped_splits(w.shape[0], kernels.sm_count(w.device)))
     x = fused_input(a, w)
     if x is not None:
         emit = None
