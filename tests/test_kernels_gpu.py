@@ -293,6 +293,62 @@ def test_gemm_tc_with_swiglu_epilogue(k, M, F, K):
     assert k.status_word("cuda").item() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(9, 328, 80), (64, 2048, 8192), (33, 5000, 64), (16, 136, 520), (64, 2048, 2048)])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_gemm_tc_writes_the_next_norms_inputs(k, M, N, K, splits):
+    """Up to 64 rows (the weights on the 128-row side): the accumulating contraction into float32 rows
+    also writes bfloat16(rows * norm weight) and the rows' sums of squares per 32 columns, with K whole
+    and cut over a cluster; a ragged last tile of weight rows."""
+    a = rnd((M, K), 1, torch.bfloat16).cuda()
+    w = rnd((N, K), 2, torch.bfloat16, 0.1).cuda()
+    nw = (1 + rnd((N,), 3, torch.float32, 0.2)).cuda()
+    bias = rnd((N,), 5, torch.float32).cuda()
+    res0 = rnd((M, N), 4, torch.float32, 2.0).cuda()
+    res, plain = res0.clone(), res0.clone()
+    emit = k.NormEmit(nw)
+    assert k.gemm_tc_emits(a, res)
+    k.gemm_tc(a, w, out=res, accumulate=True, bias=bias, splits=splits, emit=emit)
+    k.gemm_tc(a, w, out=plain, accumulate=True, bias=bias, splits=splits)
+    assert torch.equal(res, plain)                       # the sum itself is the same bits
+    close(res, a.double() @ w.double().T + bias.double() + res0.double(), torch.bfloat16, "the sum")
+    assert emit.xw.shape == (M, N) and emit.ssq.shape == (M, -(-N // 32))
+    assert torch.equal(emit.xw, (res * nw).bfloat16())
+    sq = torch.zeros((M, emit.ssq.shape[1] * 32), dtype=torch.float64, device="cuda")
+    sq[:, :N] = res.double() ** 2
+    close(emit.ssq, sq.reshape(M, -1, 32).sum(-1), torch.float32, "sums of squares per 32 columns")
+    assert k.status_word("cuda").item() == 0
+    with pytest.raises(k.KernelError):
+        k.gemm_tc(a, w, out=res.bfloat16(), accumulate=True, emit=k.NormEmit(nw))
+
+
+@pytest.mark.parametrize("M,N,K", [(9, 328, 80), (64, 6144, 2048), (33, 65536 + 32, 72), (20, 136, 520)])
+@pytest.mark.parametrize("splits", [1, 2, 8])
+def test_gemm_tc_with_prepared_norm(k, M, N, K, splits):
+    x = rnd((M, K), 1, torch.float32, 3.0).cuda()
+    x[M - 1] *= 40.0                                    # a row whose scale differs much from the others'
+    x[0] *= 0.01
+    nw = (1 + rnd((K,), 2, torch.float32, 0.1)).cuda()
+    w = rnd((N, K), 3, torch.bfloat16, 0.1).cuda()
+    ref = norm_ref(x, nw, 1e-5).bfloat16().double() @ w.double().T
+    inp = scaled_input(k, x, nw, 1e-5, parts_of=32)
+    assert k.gemm_tc_takes(inp, w)
+    got = k.gemm_tc(inp, w, out_dtype=torch.float32, splits=splits)
+    for m in range(M):     # each row against its own size: a wrong row's scale would show
+        close(got[m], ref[m], torch.bfloat16, f"row {m}")
+    bias = rnd((N,), 5, torch.float32).cuda()
+    res0 = rnd((M, N), 4, torch.float32).cuda()
+    res = res0.clone()
+    k.gemm_tc(inp, w, out=res, accumulate=True, bias=bias, splits=splits)
+    close(res, ref + bias.double() + res0.double(), torch.bfloat16, "prepared norm, bias, accumulate")
+    if N % 32 == 0:
+        F = N // 2
+        g, u = ref[:, :F], ref[:, F:]
+        h = k.gemm_tc(inp, interleaved([w[:F], w[F:]]), swiglu=True, splits=splits)
+        close(h, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "prepared norm with the SwiGLU epilogue")
+    assert k.status_word("cuda").item() == 0
+    assert not k.gemm_tc_takes(scaled_input(k, rnd((65, K), 1, torch.float32).cuda(), nw, 1e-5), w)
+
+
 @pytest.mark.parametrize("M,D,K,taps,bias,norm", [(1, 80, 80, 2, False, False), (8, 2048, 2048, 3, False, True),
                                                   (13, 96, 96, 4, True, True), (16, 48, 64, 7, True, False),
                                                   (8, 2048, 2048, 3, False, "prepared"), (5, 96, 104, 4, True, "prepared")])

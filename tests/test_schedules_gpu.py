@@ -148,33 +148,39 @@ def test_chunked_prompts_against_plain(model_folders, name, dtype, chunk):
     engine.cache.check_consistency()
 
 
+@pytest.mark.parametrize("n_seqs", [5, 12, 40])
 @pytest.mark.parametrize("name", ["loud_d", "loud_e"])
-def test_single_token_steps_of_few_sequences_prepare_their_norms(model_folders, name, monkeypatch):
-    """In bfloat16 steps of up to 8 rows the contraction that sums into the residual rows prepares the
+def test_single_token_steps_prepare_their_norms(model_folders, name, n_seqs, monkeypatch):
+    """In bfloat16 steps of up to 64 rows the contraction that sums into the residual rows prepares the
     norm that follows, for every norm of the step but the first (behind the embedding), the final
-    norm included.  The same steps with that route closed agree with the plain model as well."""
+    norm included: up to 8 rows in the mma.sync kernels, above in the tcgen05 kernel.  The same steps
+    with that route closed agree with the plain model as well."""
     import zinfer_b200 as z
     from zinfer_b200 import kernels
     from zinfer_b200.parts.norm import RMSNorm
     folder = model_folders[name]
     plain = PlainLfm2(folder, dtype=np.float64)
     vocab, n_layers = plain.cfg["vocab_size"], plain.cfg["num_hidden_layers"]
-    seqs = [helpers.random_tokens(900 + i, 9 + 3 * i + 6, vocab) for i in range(5)]
+    seqs = [helpers.random_tokens(900 + i, 9 + (3 * i) % 50 + 6, vocab) for i in range(n_seqs)]
     heads = [len(s) - 6 for s in seqs]
     ref = [plain.logits(s) for s in seqs]
-    made = []
+    made = []      # contractions that were handed rows with their norm prepared
 
-    class Counted(kernels.ScaledInput):
-        def __init__(self, *a, **kw):
-            made.append(1)
-            super().__init__(*a, **kw)
+    def counting(fn):
+        def call(a, *rest, **kw):
+            if isinstance(a, kernels.ScaledInput):
+                made.append(fn.__name__)
+            return fn(a, *rest, **kw)
+        return call
 
-    monkeypatch.setattr(kernels, "ScaledInput", Counted)
+    for fn in ("gemm_skinny", "gemm_skinny_swiglu", "gemm_skinny_conv", "gemm_tc"):
+        monkeypatch.setattr(kernels, fn, counting(getattr(kernels, fn)))
     counts = {}
     for route in ("prepared", "closed"):
         if route == "closed":
             monkeypatch.setattr(RMSNorm, "ahead", lambda self, ctx, x: None)
-        engine = z.Engine(z.load(folder, dtype="bfloat16"), max_batch=5, max_seq_len=128, page_size=64, use_graphs=False)
+        engine = z.Engine(z.load(folder, dtype="bfloat16"), max_batch=n_seqs, max_seq_len=128, page_size=64,
+                          use_graphs=False)
         made.clear()
         worst, where, sizes = drive(engine, seqs, heads, ref)
         counts[route] = len(made) / len(sizes)

@@ -44,7 +44,48 @@ struct Params {
   int M, N, K;         // M tokens, N weight rows
   int ldc, accumulate, splits;
   int swiglu;          // normal mode: W rows are groups of 16 gate rows + their 16 up rows; C [M, N/2] = silu(g)*u
+  // Up to 64 tokens only.  ssq_in: X holds bfloat16(x * norm weight) of rows whose RMSNorm is still to be
+  // applied, ssq_in [M, ssq_parts] partial sums of x^2: token t's sums are scaled by
+  // 1 / sqrt(sum(ssq_in[t]) / K + eps).  emit_x: beside C (the float32 residual rows) the kernel writes
+  // emit_x [M, N] = bfloat16(C * emit_w) and emit_ssq [M, ceil(N / 32)] = sums of C^2 over 32 columns,
+  // for the norm that reads C next.
+  const float* ssq_in;
+  int ssq_parts;
+  float eps;
+  const float* emit_w;
+  bf16* emit_x;
+  float* emit_ssq;
 };
+
+// q[j] of every lane, j < T (T = 4, 8 or 16): the sums over the warp's 32 lanes, T - 1 + log2(32 / T)
+// shuffles in place of 5 T.  Every lane returns the sum of q[token_of_lane<T>(lane)].
+template <int T>
+__device__ __forceinline__ int token_of_lane(int lane) {
+  int j = 0;
+#pragma unroll
+  for (int w = T / 2, mask = 16; w >= 1; w >>= 1, mask >>= 1)
+    if (lane & mask) j += w;
+  return j;
+}
+template <int T>
+__device__ __forceinline__ float warp_sums(float (&q)[T], int lane) {
+  int mask = 16;
+#pragma unroll
+  for (int w = T / 2; w >= 1; w >>= 1, mask >>= 1) {
+    const bool upper = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < w; ++i) {
+      const float keep = upper ? q[i + w] : q[i], send = upper ? q[i] : q[i + w];
+      q[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+    }
+  }
+  float v = q[0];
+  for (; mask >= 1; mask >>= 1) v += __shfl_xor_sync(0xffffffffu, v, mask);
+  return v;
+}
+// the lanes that write a warp_sums result: one per token
+template <int T>
+__device__ __forceinline__ bool writes_sum(int lane) { return (lane & (32 / T - 1)) == 0; }
 
 // Thread-block cluster: barrier over all threads of all blocks, rank, and loads from another
 // block's shared memory.
@@ -68,7 +109,7 @@ template <int BN, int STAGES>
 struct Smem {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr size_t BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr size_t BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers, row scales*/;
 };
 
 // SWAP = false: A tiles are 128 tokens of X, B tiles are BN weight rows; C[token][weight row].
@@ -84,6 +125,7 @@ __global__ void __launch_bounds__(THREADS)
   unsigned long long* acc_done = empty + STAGES;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_done + 1);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* row_scale = reinterpret_cast<float*>(full) + 32;   // [64], 128 bytes behind the first barrier
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a_tile = blockIdx.x, b_tile = blockIdx.y, split = blockIdx.z;
@@ -167,6 +209,27 @@ __global__ void __launch_bounds__(THREADS)
     const int quarter = warp & 3;            // the 32 accumulator lanes this warp may read
     const int row = quarter * 32 + lane;     // row of the tile
     zk_wait_prior();                         // C, which this warp reads and writes, is the kernels' before
+    if constexpr (SWAP) {
+      if (p.ssq_in) {
+        // two lanes per token add its partial sums in a fixed order; every block of a cluster does so
+        static_assert(STAGES <= 6, "the row scales lie 128 bytes behind the barriers");
+        const int e = (warp - 2) * 32 + lane, t = e >> 1;
+        float sum = 0.f;
+        if (t < p.M) {
+          const float* mine = p.ssq_in + (size_t)t * p.ssq_parts;
+          for (int q0 = e & 1; q0 < p.ssq_parts; q0 += 32) {   // 16 loads under way at a time
+            float v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = q0 + 2 * u < p.ssq_parts ? mine[q0 + 2 * u] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) sum += v[u];
+          }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if ((e & 1) == 0) row_scale[t] = t < p.M ? 1.0f / sqrtf(sum / (float)p.K + p.eps) : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+      }
+    }
     bool ok = mbar_wait(acc_done, 0);
     if (!ok) {
       if (lane == 0) atomicExch(p.status, 13);
@@ -276,7 +339,13 @@ __global__ void __launch_bounds__(THREADS)
         if (p.splits > 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = v[j];
-        } else if (p.swiglu) {
+          continue;
+        }
+        if (p.ssq_in) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] *= row_scale[c0 + j];   // BN <= 64 tokens
+        }
+        if (p.swiglu) {
           // a warp's 32 rows are 16 gate rows and their 16 up rows (N is a multiple of 32, so the
           // whole warp is on one side of N): lane l < 16 takes the up value of lane l + 16
           const int f = (n >> 5) * 16 + (n & 15);   // output column of this gate row
@@ -286,15 +355,30 @@ __global__ void __launch_bounds__(THREADS)
             if ((lane & 16) == 0 && n < p.N && c0 + j < p.M)
               C[(size_t)(c0 + j) * p.ldc + f] = from_f32<TC>(v[j] / (1.0f + expf(-v[j])) * up);
           }
-        } else if (n < p.N) {
-          const float b = p.bias ? p.bias[n] : 0.f;
+        } else {
+          const bool n_in = n < p.N;
+          const float b = (p.bias && n_in) ? p.bias[n] : 0.f;
           float old[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j)   // all loads first: they do not depend on one another
-            old[j] = (p.accumulate && c0 + j < p.M) ? to_f32(C[(size_t)(c0 + j) * p.ldc + n]) : 0.f;
+            old[j] = (p.accumulate && n_in && c0 + j < p.M) ? to_f32(C[(size_t)(c0 + j) * p.ldc + n]) : 0.f;
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c0 + j < p.M) C[(size_t)(c0 + j) * p.ldc + n] = from_f32<TC>(v[j] + b + old[j]);
+          for (int j = 0; j < 16; ++j) {
+            v[j] = (n_in && c0 + j < p.M) ? v[j] + b + old[j] : 0.f;
+            if (n_in && c0 + j < p.M) C[(size_t)(c0 + j) * p.ldc + n] = from_f32<TC>(v[j]);
+          }
+          if (p.emit_x) {   // float32 C: v is what was stored
+            const float nw = n_in ? p.emit_w[n] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (n_in && c0 + j < p.M) p.emit_x[(size_t)(c0 + j) * p.N + n] = __float2bfloat16_rn(v[j] * nw);
+              v[j] *= v[j];
+            }
+            const float sq = warp_sums<16>(v, lane);
+            const int t = c0 + token_of_lane<16>(lane);
+            if (writes_sum<16>(lane) && t < p.M && a_tile * BM + quarter * 32 < p.N)
+              p.emit_ssq[(size_t)t * ((p.N + 31) / 32) + a_tile * (BM / 32) + quarter] = sq;
+          }
         }
       }
     }
@@ -312,46 +396,61 @@ __global__ void __launch_bounds__(THREADS)
         TC* C = reinterpret_cast<TC*>(p.C);
         const unsigned base = smem_u32(tiles);
         const unsigned rank = cluster_rank();
-        if (n < p.N) {
-          const float b = p.bias ? p.bias[n] : 0.f;
-          // The remote partials and old values of 32 / splits tokens (32 loads from the cluster's
-          // shared memory and up to 16 from global memory) are all requested before the first sum,
-          // so a thread waits for them once, not once per token: with four tokens at a time the
-          // loop took longer than the contraction when K was split in two.
-          auto reduce = [&](auto splits_c) {
-            constexpr int SP = decltype(splits_c)::value, TOK = 32 / SP;
-            for (int t0 = (int)rank; t0 < p.M; t0 += TOK * SP) {
-              float pv[TOK][SP], old[TOK];
+        const bool n_in = n < p.N;
+        const float b = (p.bias && n_in) ? p.bias[n] : 0.f;
+        const float nw = (p.emit_x && n_in) ? p.emit_w[n] : 0.f;
+        // The remote partials and old values of 32 / splits tokens (32 loads from the cluster's
+        // shared memory and up to 16 from global memory) are all requested before the first sum,
+        // so a thread waits for them once, not once per token: with four tokens at a time the
+        // loop took longer than the contraction when K was split in two.
+        auto reduce = [&](auto splits_c) {
+          constexpr int SP = decltype(splits_c)::value, TOK = 32 / SP;
+          for (int t0 = (int)rank; t0 < p.M; t0 += TOK * SP) {
+            float pv[TOK][SP], old[TOK];
 #pragma unroll
-              for (int i = 0; i < TOK; ++i) {
-                const int t = t0 + i * SP;
+            for (int i = 0; i < TOK; ++i) {
+              const int t = t0 + i * SP;
 #pragma unroll
-                for (int z = 0; z < SP; ++z)
-                  pv[i][z] = t < p.M ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
-                old[i] = (t < p.M && p.accumulate) ? to_f32(C[(size_t)t * p.ldc + n]) : 0.f;
-              }
+              for (int z = 0; z < SP; ++z)
+                pv[i][z] = t < p.M ? ld_remote_f32(base + (unsigned)(t * BM + row) * 4u, (unsigned)z) : 0.f;
+              old[i] = (t < p.M && n_in && p.accumulate) ? to_f32(C[(size_t)t * p.ldc + n]) : 0.f;
+            }
+            float sq[TOK];
 #pragma unroll
-              for (int i = 0; i < TOK; ++i) {
-                const int t = t0 + i * SP;
-                if (t >= p.M) break;
-                float acc = b;
+            for (int i = 0; i < TOK; ++i) {
+              const int t = t0 + i * SP;
+              sq[i] = 0.f;
+              if (t >= p.M) continue;        // the same for every lane
+              float acc = 0.f;
 #pragma unroll
-                for (int z = 0; z < SP; ++z) acc += pv[i][z];
-                if (p.swiglu) {
-                  // as in the unsplit epilogue: a warp's rows are 16 gate rows and their 16 up rows
-                  const float up = __shfl_down_sync(0xffffffffu, acc, 16);
-                  if ((lane & 16) == 0)
-                    C[(size_t)t * p.ldc + (n >> 5) * 16 + (n & 15)] = from_f32<TC>(acc / (1.0f + expf(-acc)) * up);
-                } else {
-                  C[(size_t)t * p.ldc + n] = from_f32<TC>(acc + old[i]);
+              for (int z = 0; z < SP; ++z) acc += pv[i][z];
+              if (p.ssq_in) acc *= row_scale[t];
+              acc += b;
+              if (p.swiglu) {
+                // as in the unsplit epilogue: a warp's rows are 16 gate rows and their 16 up rows
+                const float up = __shfl_down_sync(0xffffffffu, acc, 16);
+                if ((lane & 16) == 0 && n_in)
+                  C[(size_t)t * p.ldc + (n >> 5) * 16 + (n & 15)] = from_f32<TC>(acc / (1.0f + expf(-acc)) * up);
+              } else if (n_in) {
+                acc += old[i];
+                C[(size_t)t * p.ldc + n] = from_f32<TC>(acc);
+                if (p.emit_x) {
+                  p.emit_x[(size_t)t * p.N + n] = __float2bfloat16_rn(acc * nw);
+                  sq[i] = acc * acc;
                 }
               }
             }
-          };
-          if (p.splits == 2) reduce(std::integral_constant<int, 2>());
-          else if (p.splits == 4) reduce(std::integral_constant<int, 4>());
-          else reduce(std::integral_constant<int, 8>());
-        }
+            if (p.emit_x) {
+              const float total = warp_sums<TOK>(sq, lane);
+              const int t = t0 + token_of_lane<TOK>(lane) * SP;
+              if (writes_sum<TOK>(lane) && t < p.M && a_tile * BM + (warp & 3) * 32 < p.N)
+                p.emit_ssq[(size_t)t * ((p.N + 31) / 32) + a_tile * (BM / 32) + (warp & 3)] = total;
+            }
+          }
+        };
+        if (p.splits == 2) reduce(std::integral_constant<int, 2>());
+        else if (p.splits == 4) reduce(std::integral_constant<int, 4>());
+        else reduce(std::integral_constant<int, 8>());
       }
       __syncwarp();
       cluster_sync_all();   // nobody leaves while its shared memory may still be read
@@ -758,11 +857,18 @@ extern "C" {
 // X [M, K], W [N, K] bfloat16, K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
 // M <= 64 runs swapped (weights on the 128-row side) with K cut into `splits` parts (rounded down
 // to 1, 2, 4 or 8: a cluster's size); larger M runs normal and ignores splits.  With `swiglu`
-// (not with split K) W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2]
-// receives silu(gate) * up (src/model.zig:1085-1117).
+// W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2] receives
+// silu(gate) * up (src/model.zig:1085-1117).  M <= 64 only: ssq_in [M, ssq_parts] (or null) says
+// that X is bfloat16(x * norm weight) and scales token t's sums by 1 / sqrt(sum(ssq_in[t]) / K +
+// eps); emit_x (or null; float32 C, no SwiGLU) is written as bfloat16(C * emit_w), [M, N], and
+// emit_ssq [M, ceil(N / 32)] as the sums of C^2 over 32 columns.
 int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
-               int out_dtype, int accumulate, int splits, int swiglu, int* status, cudaStream_t stream) {
+               int out_dtype, int accumulate, int splits, int swiglu, const float* ssq_in, int ssq_parts, float eps,
+               const float* emit_w, void* emit_x, float* emit_ssq, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if ((ssq_in || emit_x) && M > 64) return ZK_EINVAL;
+  if (ssq_in && ssq_parts <= 0) return ZK_EINVAL;
+  if (emit_x && (!emit_w || !emit_ssq || swiglu || out_dtype != ZK_F32)) return ZK_EINVAL;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < (swiglu ? N / 2 : N) || !status) return ZK_EINVAL;
   if (swiglu && (N % 32 || bias || accumulate)) return ZK_EINVAL;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
@@ -770,6 +876,8 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   Params p{};
   p.C = C; p.bias = bias; p.status = status;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1; p.swiglu = swiglu;
+  p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.eps = eps;
+  p.emit_w = emit_w; p.emit_x = (bf16*)emit_x; p.emit_ssq = emit_ssq;
   CUtensorMap ma, mb, mc;
   const bool f32 = out_dtype == ZK_F32;
   if (M > 64) {

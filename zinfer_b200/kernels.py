@@ -39,7 +39,7 @@ _SIGNATURES = {
         "zk_gemm_skinny_fused_max_m": "",
     },
     "gemm_tc": {
-        "zk_gemm_tc": "ppppiiiiiiiiiipp",
+        "zk_gemm_tc": "ppppiiiiiiiiii" + "pifppp" + "pp",
         "zk_gemm_tc_force_form": "i",
     },
     "shortconv": {
@@ -261,9 +261,16 @@ def status_word(device) -> torch.Tensor:
     return st["status"]
 
 
-def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
+GEMM_TC_SWAPPED_MAX_M = 64     # up to this many rows the weights take the 128-row side of the tiles
+
+
+def gemm_tc_takes(a, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
     """Whether the tcgen05 kernel takes this contraction: bfloat16, K a multiple of 8, rows and
-    output 16-byte aligned."""
+    output 16-byte aligned.  `a` is a bfloat16 tensor, or a ScaledInput of up to 64 rows."""
+    if isinstance(a, ScaledInput):
+        if a.xw.shape[0] > GEMM_TC_SWAPPED_MAX_M or not a.ssq.is_contiguous():
+            return False
+        a = a.xw
     ok = (isinstance(a, torch.Tensor) and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2
           and w.dim() == 2 and a.shape[1] == w.shape[1] and a.shape[1] % 8 == 0 and a.stride(1) == 1
           and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
@@ -273,19 +280,30 @@ def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     return ok
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
+def gemm_tc_emits(a, out: Optional[torch.Tensor]) -> bool:
+    """Whether `gemm_tc` can write a NormEmit beside `out` for this input."""
+    return (a.shape[0] <= GEMM_TC_SWAPPED_MAX_M and out is not None and out.dtype == torch.float32
+            and out.is_contiguous())
+
+
+def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
             accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1,
-            swiglu: bool = False) -> torch.Tensor:
+            swiglu: bool = False, emit: Optional["NormEmit"] = None) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
     More than 64 rows: persistent blocks on 256-wide tiles when N is a multiple of 256 (pairs of
     blocks with tcgen05.mma.cta_group::2 above 128 rows, TMA stores), else one 128 x 128 tile of
     tokens x weight rows per block.  Up to 64 rows: the weights take
     the 128-row side and K is cut into `splits` (1, 2, 4 or 8) parts, one per block of a cluster,
     that are added in order.  With `swiglu` w holds groups of 16 gate rows and
-    their 16 up rows and the result is silu(gate) * up, [M, N/2]."""
+    their 16 up rows and the result is silu(gate) * up, [M, N/2].  Up to 64 rows `a` may be a
+    ScaledInput (the sums are scaled by the rows' 1/rms) and `emit` (see `gemm_tc_emits`) is filled
+    for the norm that reads `out` next."""
     if not gemm_tc_takes(a, w, out):
         raise KernelError(f"gemm_tc: a {tuple(a.shape)} / w {tuple(w.shape)} need bfloat16, K a multiple of 8 and "
                           "16-byte aligned rows")
+    ssq, ssq_parts, eps = None, 0, 0.0
+    if isinstance(a, ScaledInput):
+        ssq, ssq_parts, eps, a = _ptr(a.ssq), a.ssq.shape[1], a.eps, a.xw
     M, K = a.shape
     N = w.shape[0]
     if swiglu and (N % 32 or accumulate or bias is not None):
@@ -298,9 +316,18 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     _need(out, "out", (torch.float32, torch.bfloat16), (M, n_out))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
+    if emit is not None:
+        if not gemm_tc_emits(a, out) or swiglu:
+            raise KernelError("gemm_tc: the norm's inputs are written for at most 64 rows summed into contiguous "
+                              "float32 rows")
+        _need(emit.weight, "norm weight", torch.float32, (N,))
+        emit.xw = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+        emit.ssq = torch.empty((M, -(-N // 32)), dtype=torch.float32, device=w.device)
     _check(_fn("gemm_tc", "zk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), _ptr(bias), M, N, K, a.stride(0), w.stride(0),
                                         out.stride(0), dtype_code(out.dtype), 1 if accumulate else 0, splits,
-                                        1 if swiglu else 0, _ptr(status_word(a.device)), _stream()),
+                                        1 if swiglu else 0, ssq, ssq_parts, eps,
+                                        _ptr(emit.weight) if emit else None, _ptr(emit.xw) if emit else None,
+                                        _ptr(emit.ssq) if emit else None, _ptr(status_word(a.device)), _stream()),
            "gemm_tc")
     return out
 
@@ -353,7 +380,8 @@ class ScaledInput:
 
 class NormEmit:
     """What an accumulating contraction into the residual rows writes for the norm that reads them
-    next: `weight` [N] of that norm; after the call `xw` [M, N] and `ssq` [M, ceil(N / 16)]."""
+    next: `weight` [N] of that norm; after the call `xw` [M, N] = bfloat16(rows * weight) and `ssq`
+    [M, parts], partial sums of the rows' squares (how many parts is the kernel's business)."""
 
     def __init__(self, weight: torch.Tensor):
         self.weight = weight

@@ -8,7 +8,7 @@ import torch
 
 from .. import kernels
 from .base import FEED_FORWARDS, FeedForward, WeightSpec
-from .linear import FUSION_GROUP, as_tensor, fused_input, interleave_rows, linear
+from .linear import FUSION_GROUP, as_tensor, fused_input, interleave_rows, linear, scaled_or_tensor
 from .linear_bf16 import TC_SWAPPED_MIN_ROWS, swapped_splits
 
 
@@ -44,11 +44,14 @@ class SwiGLU(FeedForward):
             if x is not None:                       # few rows: gate, up and the activation in one kernel
                 h = kernels.gemm_skinny_swiglu(x, w)
             else:
-                x = as_tensor(xn)
+                x = scaled_or_tensor(xn) if tc_rows else as_tensor(xn)
+                if not kernels.gemm_tc_takes(x, w):
+                    x = as_tensor(xn)
                 rows = x.shape[0]
                 # prompt steps, and steps of 9..64 rows: activation in the epilogue
                 if (rows > kernels.gemm_skinny_max_m() or tc_rows) and kernels.gemm_tc_takes(x, w):
-                    h = kernels.gemm_tc(x, w, swiglu=True, splits=swapped_splits(w.shape[0], kernels.sm_count(w.device)) if tc_rows else 1)
+                    splits = swapped_splits(w.shape[0], kernels.sm_count(w.device)) if tc_rows else 1
+                    h = kernels.gemm_tc(x, w, swiglu=True, splits=splits)
         if h is None:
             h = kernels.silu_mul(linear(xn, w), self.interleave)
         linear(h, self.w_down, out=out, accumulate=accumulate)

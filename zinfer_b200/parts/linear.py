@@ -74,6 +74,14 @@ def as_tensor(a: Union[torch.Tensor, NormedRows]) -> torch.Tensor:
     return a.tensor() if isinstance(a, NormedRows) else a
 
 
+def scaled_or_tensor(a: Union[torch.Tensor, NormedRows]):
+    """For a kernel that takes a `kernels.ScaledInput`: that, if the rows came prepared and nobody
+    has asked for the normalised tensor yet; else the tensor."""
+    if isinstance(a, NormedRows) and a.scaled is not None and a._tensor is None and a.dtype == torch.bfloat16:
+        return kernels.ScaledInput(a.scaled.xw, a.scaled.ssq, a.eps)
+    return as_tensor(a)
+
+
 # A block that applies the norm itself reads all M rows again, so fusing the norm pays only while
 # few blocks do so (about one per SM) or the rows are very few; measured on the LFM2-1.2B shapes:
 # fused 12.5 us against 14.5 us for the short convolution's in_proj (128 blocks, 8 rows), but
@@ -102,6 +110,9 @@ def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_
             worth = n_blocks <= NORM_FUSION_MAX_BLOCKS or a.shape[0] <= NORM_FUSION_ANY_BLOCKS_ROWS
             if worth and takes(ki, w):
                 return ki
+            max_rows = kernels.gemm_skinny_fused_max_m() if need_fused_rows else kernels.gemm_skinny_max_m()
+            if a.shape[0] > max_rows:
+                return None             # too many rows for these kernels: the norm stays pending for another
         a = a.tensor()
     return a if takes(a, w) else None
 

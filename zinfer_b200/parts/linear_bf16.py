@@ -30,13 +30,21 @@ def swapped_splits(n_weight_rows: int, sm_count: int) -> int:
 
 
 def try_linear(a, w, out, out_dtype, accumulate, bias, sink=None):
-    from .linear import as_tensor, fused_input
+    from .linear import as_tensor, fused_input, scaled_or_tensor
 
     if TC_SWAPPED_MIN_ROWS <= a.shape[0] <= kernels.gemm_skinny_max_m():
-        t = as_tensor(a)
+        t = scaled_or_tensor(a)
+        if not kernels.gemm_tc_takes(t, w, out):
+            t = as_tensor(a)
         if kernels.gemm_tc_takes(t, w, out):
-            return kernels.gemm_tc(t, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias,
-                                   splits=swapped_splits(w.shape[0], kernels.sm_count(w.device)))
+            emit = None
+            if sink is not None and kernels.gemm_tc_emits(t, out):
+                emit = kernels.NormEmit(sink.norm_weight)
+            y = kernels.gemm_tc(t, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias,
+                                splits=swapped_splits(w.shape[0], kernels.sm_count(w.device)), emit=emit)
+            if emit is not None:
+                sink.emit = emit
+            return y
     x = fused_input(a, w)
     if x is not None:
         emit = None

@@ -37,7 +37,7 @@ class RMSNorm(Norm):
     def ahead(self, ctx, x):
         """For the few rows of a single-token step in bfloat16: the contraction that sums into `x`
         can write this norm's inputs along (see `linear`)."""
-        if ctx.dtype != torch.bfloat16 or x.shape[0] > kernels.GEMM_SKINNY_EMIT_MAX_M:
+        if ctx.dtype != torch.bfloat16 or x.shape[0] > kernels.GEMM_TC_SWAPPED_MAX_M:
             return None
         return ResidualSink(x, self.weight)
 
