@@ -5,8 +5,8 @@
 // tile (rows G..15 are zero), so one pass over the K and V of a KV head serves all of them (the
 // reference orders the queries of a KV head the same way, src/model.zig:1352-1366).  A block owns
 // (sequence, KV head, chunk of keys).  Its keys are walked in tiles of 64 that lie inside one cache
-// page; the four warps bring a tile in together with cp.async into XOR-swizzled shared memory,
-// double-buffered, and then each warp takes 16 of the tile's keys: S = Q K^T from ldmatrix
+// page; the four warps bring a tile in together with cp.async into XOR-swizzled shared memory
+// (a ring of two to four tile buffers), and then each warp takes 16 of the tile's keys: S = Q K^T from ldmatrix
 // fragments, online softmax (src/attention.zig:478-517, no tile skipped), O += P V.  The warps'
 // (m, l, o) are merged in shared memory and written either as the result (one chunk) or as a
 // partial for `zk_attn_merge` (src/model.zig:1941-1955, src/attention.zig:749-814).
@@ -59,7 +59,7 @@ __device__ __forceinline__ int swz(int r, int ch) {
 }
 
 // HD: head_dim, 64 or 128 (rows of a tile are whole 128-byte lines, which the swizzle assumes).
-template <int HD>
+template <int HD, int NST>
 __global__ void __launch_bounds__(DT_WARPS * 32)
     attn_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                           bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -70,8 +70,8 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   constexpr int CH = HD / 8;                // 16-byte chunks per row
   constexpr int TILE_BYTES = DT_TK * HD * 2;
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Ksm[2] = {smem, smem + 2 * TILE_BYTES};
-  unsigned char* Vsm[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES};
+  auto Ksm = [&](int buf) { return smem + (size_t)(2 * buf) * TILE_BYTES; };
+  auto Vsm = [&](int buf) { return smem + (size_t)(2 * buf + 1) * TILE_BYTES; };
 
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -110,8 +110,8 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       const int r = i / CH, ch = i % CH;
       const bool valid = page >= 0 && kb + r < c1;
       const size_t off = base + (size_t)(valid ? r : 0) * HD + ch * 8;
-      cp_async16(Ksm[buf] + swz<HD>(r, ch), k_cache + off, valid);
-      cp_async16(Vsm[buf] + swz<HD>(r, ch), v_cache + off, valid);
+      cp_async16(Ksm(buf) + swz<HD>(r, ch), k_cache + off, valid);
+      cp_async16(Vsm(buf) + swz<HD>(r, ch), v_cache + off, valid);
     }
     cp_async_commit();
   };
@@ -123,15 +123,18 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
-  if (n_tiles > 0) load_tile(0, 0);
+  // NST buffers: tiles t + 1 .. t + NST - 1 are under way while tile t is worked on.  Every
+  // iteration commits one group (an empty one when no tile is left), so "all but the newest
+  // NST - 1 groups" is always "tile t has landed".
+  for (int t = 0; t < NST - 1; ++t) {
+    if (t < n_tiles) load_tile(t, t);
+    else cp_async_commit();
+  }
   for (int t = 0; t < n_tiles; ++t) {
-    const int buf = t & 1;
-    if (t + 1 < n_tiles) {
-      load_tile(t + 1, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int buf = t % NST;
+    if (t + NST - 1 < n_tiles) load_tile(t + NST - 1, (t + NST - 1) % NST);
+    else cp_async_commit();
+    cp_async_wait<NST - 1>();
     __syncthreads();
     const int kb = k_begin + t * DT_TK + 16 * warp;   // this warp's 16 keys of the tile
 
@@ -145,7 +148,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       for (int ks = 0; ks < KS; ks += 2) {
         unsigned bfr[4];
         const int r = 16 * warp + 8 * j + (lane & 7), ch = 2 * ks + (lane >> 3);
-        ldmatrix_x4(bfr, Ksm[buf] + swz<HD>(r, ch));
+        ldmatrix_x4(bfr, Ksm(buf) + swz<HD>(r, ch));
         mma16816(s[j], qf[ks], bfr[0], bfr[1]);
         mma16816(s[j], qf[ks + 1], bfr[2], bfr[3]);
       }
@@ -203,13 +206,14 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     for (int jn = 0; jn < HD / 8; jn += 2) {
       unsigned bfr[4];
       const int r = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8, ch = jn + (lane >> 4);
-      ldmatrix_x4_trans(bfr, Vsm[buf] + swz<HD>(r, ch));
+      ldmatrix_x4_trans(bfr, Vsm(buf) + swz<HD>(r, ch));
       mma16816(o[jn], pa, bfr[0], bfr[1]);
       mma16816(o[jn + 1], pa, bfr[2], bfr[3]);
     }
     __syncthreads();  // the tile is consumed before the next load overwrites its buffer
   }
 
+  cp_async_wait<0>();   // only empty groups are left
   // merge the four warps' partial results in shared memory (the tile buffers are free now)
   float* sm_m = reinterpret_cast<float*>(smem);              // [warps][16]
   float* sm_l = sm_m + DT_WARPS * 16;                        // [warps][16]
@@ -254,13 +258,13 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   }
 }
 
-template <int HD>
+template <int HD, int NST>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
            const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H, int Hkv,
            int page_size, int window, float scale, int num_splits, int split_keys, cudaStream_t stream) {
-  auto kern = attn_decode_tc_kernel<HD>;
-  const size_t smem = 4 * (size_t)DT_TK * HD * 2;
-  static_assert(4 * DT_TK * HD * 2 >= (2 * DT_WARPS * 16 + DT_WARPS * 16 * HD) * 4, "the merge fits in the tile buffers");
+  auto kern = attn_decode_tc_kernel<HD, NST>;
+  const size_t smem = 2 * NST * (size_t)DT_TK * HD * 2;
+  static_assert(2 * NST * DT_TK * HD * 2 >= (2 * DT_WARPS * 16 + DT_WARPS * 16 * HD) * 4, "the merge fits in the tile buffers");
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -293,10 +297,18 @@ int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, v
   if (n_seqs <= 0) return 0;
   if (!zk_attn_decode_tc_takes(H, Hkv, hd, page_size) || num_splits < 1) return ZK_EINVAL;
   if (num_splits > 1 && (split_keys <= 0 || split_keys % DT_TK || !part_o || !part_ml)) return ZK_EINVAL;
+  // Tile buffers (head_dim 64): a block whose chunk is at most four tiles asks for all of them at once;
+  // longer chunks keep two tiles under way behind the one being worked on.  Measured on whole steps of
+  // the LFM2-1.2B shape: 8 sequences (chunks of three tiles) 0.707 ms with two buffers, 0.720 with three,
+  // 0.695 with four; 64 sequences (chunks of some ten tiles) 1.55, 1.53 and 1.57 ms.
+  const bool short_chunks = num_splits > 1 && split_keys <= 4 * DT_TK;
+  if (hd == 64 && short_chunks)
+    return launch<64, 4>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
+                         Hkv, page_size, window, scale, num_splits, split_keys, stream);
   if (hd == 64)
-    return launch<64>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
+    return launch<64, 3>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
                       Hkv, page_size, window, scale, num_splits, split_keys, stream);
-  return launch<128>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
+  return launch<128, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
                      Hkv, page_size, window, scale, num_splits, split_keys, stream);
 }
 
