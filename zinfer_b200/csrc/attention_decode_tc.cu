@@ -298,16 +298,18 @@ int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, v
   if (!zk_attn_decode_tc_takes(H, Hkv, hd, page_size) || num_splits < 1) return ZK_EINVAL;
   if (num_splits > 1 && (split_keys <= 0 || split_keys % DT_TK || !part_o || !part_ml)) return ZK_EINVAL;
   // Tile buffers (head_dim 64): a block whose chunk is at most four tiles asks for all of them at once;
-  // longer chunks keep two tiles under way behind the one being worked on.  Measured on whole steps of
-  // the LFM2-1.2B shape: 8 sequences (chunks of three tiles) 0.707 ms with two buffers, 0.720 with three,
-  // 0.695 with four; 64 sequences (chunks of some ten tiles) 1.55, 1.53 and 1.57 ms.
+  // longer chunks are double-buffered, because more blocks on an SM hide more latency than a deeper
+  // ring in fewer blocks.  Measured on whole steps, two / three / four buffers: LFM2-1.2B shape with 8
+  // sequences (chunks of three tiles) 0.707 / 0.720 / 0.695 ms; with 64 sequences (chunks of some ten
+  // tiles) 1.55 / 1.53 / 1.57 ms; LFM2-350M shape with 64 sequences of up to 32,768 tokens (chunks of
+  // 4,096 keys) 3.41 / 3.72 / 4.16 ms.
   const bool short_chunks = num_splits > 1 && split_keys <= 4 * DT_TK;
   if (hd == 64 && short_chunks)
     return launch<64, 4>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
                          Hkv, page_size, window, scale, num_splits, split_keys, stream);
   if (hd == 64)
-    return launch<64, 3>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                      Hkv, page_size, window, scale, num_splits, split_keys, stream);
+    return launch<64, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
+                         Hkv, page_size, window, scale, num_splits, split_keys, stream);
   return launch<128, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
                      Hkv, page_size, window, scale, num_splits, split_keys, stream);
 }
