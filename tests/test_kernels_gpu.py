@@ -474,6 +474,41 @@ def test_short_conv_packed_and_stepwise(k, dtype, D, K, use_bias):
         close(y2[3 * i:3 * i + 3], whole[0][-3:], dtype, f"conv continued prompt seq {i}")
 
 
+@pytest.mark.parametrize("D,K,use_bias,il", [(96, 3, False, 16), (200, 2, True, 0), (64, 4, True, 16), (2048, 3, False, 16)])
+def test_short_conv_of_many_packed_tokens(k, D, K, use_bias, il):
+    """Prompt steps of 256 tokens and more in bfloat16 (runs of tokens per thread): sequences of unequal
+    lengths whose borders fall inside a run, states that are not zero (continued prompts); against the
+    reference, and the same bits as each sequence alone in a step of few tokens (the other kernel)."""
+    lens = [1, 2, 131, K - 1, 77, 3, 202, 5]
+    slots = [4, 0, 2, 7, 1, 8, 3, 6]
+    n_slots = 9
+    taps = rnd((K, D), 11, torch.float32).cuda()
+    bias = rnd((D,), 12, torch.float32).cuda() if use_bias else None
+    seqs = [rnd((l, 3 * D), 20 + i, torch.bfloat16) for i, l in enumerate(lens)]
+    state = rnd((n_slots, K - 1, D), 13, torch.float32).cuda()
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    assert cu[-1] >= 256
+    tok_seq = torch.from_numpy(np.repeat(np.arange(len(lens)), lens).astype(np.int32)).cuda()
+    seq_slot = torch.tensor(slots, dtype=torch.int32).cuda()
+
+    def stored(rows):      # the column order the kernel is told about
+        if not il:
+            return rows.cuda()
+        return interleaved([rows[:, :D].T.contiguous(), rows[:, D:2 * D].T.contiguous(),
+                            rows[:, 2 * D:].T.contiguous()]).T.contiguous().cuda()
+
+    y = k.conv_forward(stored(torch.cat(seqs)), state, taps, bias, tok_seq, torch.from_numpy(cu).cuda(), seq_slot,
+                       interleave=il)
+    for i, sq in enumerate(seqs):
+        ref, _ = conv_ref(sq.double(), taps.double().cpu(), None if bias is None else bias.double().cpu(),
+                          state[slots[i]].double().cpu())
+        close(y[cu[i]:cu[i + 1]], ref, torch.bfloat16, f"sequence {i} of the packed step")
+        if lens[i] < 256:
+            alone = k.conv_forward(stored(sq), state, taps, bias, torch.zeros(lens[i], dtype=torch.int32).cuda(),
+                                   torch.tensor([0, lens[i]], dtype=torch.int32).cuda(), seq_slot[i:i + 1], interleave=il)
+            assert torch.equal(alone, y[cu[i]:cu[i + 1]]), f"sequence {i}: packed and alone differ"
+
+
 # ------------------------------------------------------------------------------- attention
 
 def rope_ref(x, pos, inv_freq, interleaved=False):

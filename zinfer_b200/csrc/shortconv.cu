@@ -108,6 +108,92 @@ __global__ void conv_forward_vec8_kernel(const bf16* __restrict__ bcx, const flo
   *reinterpret_cast<uint4*>(y + (size_t)t * D + ch) = *reinterpret_cast<const uint4*>(o);
 }
 
+// The same bits from one thread per (RUN consecutive tokens, 8 adjacent channels), K a template
+// parameter: every B, X and C value is loaded once per thread that needs it (RUN + K - 1 rows of B
+// and X for RUN tokens, where the kernel above loads K rows per token), all loads are under way
+// before the first is used, and the taps are loaded once.  A run may cross from one sequence of the
+// packed prompts into the next: each token looks up its own sequence, and takes what lies before
+// the sequence's first token of this step from the state.
+template <int K, int RUN>
+__global__ void __launch_bounds__(128)
+    conv_forward_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__ state, const float* __restrict__ w,
+                            const float* __restrict__ bias, const int* __restrict__ tok_seq,
+                            const int* __restrict__ cu_q, const int* __restrict__ seq_slot, bf16* __restrict__ y,
+                            int n_tokens, int D, long long state_slot_stride, int il) {
+  const int ch = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  const int t0 = blockIdx.x * RUN;
+  zk_let_next_start();
+  zk_wait_prior();   // bcx is the kernel before's result, and the state is read or written by it
+  if (ch >= D || t0 >= n_tokens) return;
+  const size_t cb = bcx_col(0, ch, D, il), cc = bcx_col(1, ch, D, il), cx = bcx_col(2, ch, D, il);
+  constexpr int ROWS = RUN + K - 1;    // tokens t0 - (K - 1) .. t0 + RUN - 1
+  uint4 braw[ROWS], xraw[ROWS], craw[RUN];
+#pragma unroll
+  for (int j = 0; j < ROWS; ++j) {
+    const int tt = t0 - (K - 1) + j;
+    const bool in = tt >= 0 && tt < n_tokens;
+    const bf16* row = bcx + (size_t)(in ? tt : t0) * 3 * D;
+    braw[j] = *reinterpret_cast<const uint4*>(row + cb);
+    xraw[j] = *reinterpret_cast<const uint4*>(row + cx);
+  }
+#pragma unroll
+  for (int r = 0; r < RUN; ++r)
+    craw[r] = *reinterpret_cast<const uint4*>(bcx + (size_t)min(t0 + r, n_tokens - 1) * 3 * D + cc);
+  float wk[K][8];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const float4* wp = reinterpret_cast<const float4*>(w + (size_t)k * D + ch);
+    const float4 wa = wp[0], wc = wp[1];
+    wk[k][0] = wa.x, wk[k][1] = wa.y, wk[k][2] = wa.z, wk[k][3] = wa.w;
+    wk[k][4] = wc.x, wk[k][5] = wc.y, wk[k][6] = wc.z, wk[k][7] = wc.w;
+  }
+  float bs[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) bs[e] = bias ? bias[ch + e] : 0.f;
+  float u[ROWS][8];
+#pragma unroll
+  for (int j = 0; j < ROWS; ++j) {
+    float bv[8], xv[8];
+    unpack_bf16x8(braw[j], bv);
+    unpack_bf16x8(xraw[j], xv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) u[j][e] = bv[e] * xv[e];
+  }
+#pragma unroll
+  for (int r = 0; r < RUN; ++r) {
+    const int t = t0 + r;
+    if (t >= n_tokens) break;
+    const int b = tok_seq[t];
+    const int i = t - cu_q[b];            // the token's place in its sequence's part of this step
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int j = i - (K - 1) + k;
+      if (j >= 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[k][e], u[r + k][e], acc[e]);
+      } else {
+        const float4* sp =
+            reinterpret_cast<const float4*>(state + (size_t)seq_slot[b] * state_slot_stride + (size_t)(K - 1 + j) * D + ch);
+        const float4 a = sp[0], c = sp[1];
+        const float us[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[k][e], us[e], acc[e]);
+      }
+    }
+    float cv[8];
+    unpack_bf16x8(craw[r], cv);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      o[e] = __floats2bfloat162_rn(cv[2 * e] * (bias ? acc[2 * e] + bs[2 * e] : acc[2 * e]),
+                                   cv[2 * e + 1] * (bias ? acc[2 * e + 1] + bs[2 * e + 1] : acc[2 * e + 1]));
+    *reinterpret_cast<uint4*>(y + (size_t)t * D + ch) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // One thread per (sequence, channel): state <- last K-1 values of u, older state rows survive
 // when the step brought fewer than K-1 tokens (src/model.zig:2020).  Row r of the new state
 // comes from row r + Tq of the old one, which lies above r, so rows are rewritten in
@@ -176,6 +262,18 @@ int zk_conv_forward(const void* bcx, const float* state, const float* w, const f
   if (dtype == ZK_BF16 && D % 8 == 0 && il % 8 == 0 && state_slot_stride % 4 == 0 &&
       (reinterpret_cast<uintptr_t>(bcx) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(state) |
        reinterpret_cast<uintptr_t>(w)) % 16 == 0) {
+    // many tokens and few taps: runs of four tokens per thread
+    constexpr int RUN = 4;
+    if (n_tokens >= 256 && K <= 4) {
+      dim3 grid_run(ceil_div_i(n_tokens, RUN), ceil_div_i(D / 8, threads));
+#define ZK_CONV_RUN(KV)                                                                                              \
+  return zk_launch_dependent(conv_forward_run_kernel<KV, RUN>, grid_run, dim3(threads), 0, stream, (const bf16*)bcx, \
+                             state, w, bias, tok_seq, cu_q, seq_slot, (bf16*)y, n_tokens, D, state_slot_stride, il);
+      if (K == 2) { ZK_CONV_RUN(2) }
+      if (K == 3) { ZK_CONV_RUN(3) }
+      ZK_CONV_RUN(4)
+#undef ZK_CONV_RUN
+    }
     dim3 grid8(n_tokens, ceil_div_i(D / 8, threads));
     return zk_launch_dependent(conv_forward_vec8_kernel, grid8, dim3(threads), 0, stream, (const bf16*)bcx, state, w, bias,
                                tok_seq, cu_q, seq_slot, (bf16*)y, n_tokens, D, K, state_slot_stride, il);
