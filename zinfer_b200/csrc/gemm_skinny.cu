@@ -452,13 +452,21 @@ template <int NORM_MODE, typename TC>
 int dispatch_plain(const Args& a, cudaStream_t stream) {
   const bool few = a.N <= 16 * 148 * 2;    // at most two 16-row blocks per SM: make each block wider in K
   const bool many = a.N >= 16 * 148 * 6;   // many blocks: 32 rows each
+  // A warp of a 16-warp block owns K / 16 columns: from K = 4096 on that is 8 slabs and more, and all 8
+  // are requested at once (128 registers a thread, one block per SM).  Measured on whole steps of the
+  // LFM2-1.2B shape, whose w2 has K = 8192: 0.5810 -> 0.5728 ms at one row, 0.7015 -> 0.6945 ms at 8.
+  const bool long_k = a.K >= 4096;
   if (a.M <= 8) {
     if constexpr (NORM_MODE == NORM_NONE && std::is_same<TC, float>::value) {
       if (a.emit_x) {
+        if (few && long_k) return launch<16, 1, 1, 8, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
         if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
         if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
         return launch<8, 1, 1, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
       }
+    }
+    if constexpr (NORM_MODE == NORM_NONE) {
+      if (few && long_k) return launch<16, 1, 1, 8, EPI_PLAIN, NORM_NONE, TC>(a, stream);
     }
     if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
     if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
