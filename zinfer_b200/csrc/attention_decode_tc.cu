@@ -102,16 +102,36 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   const int k_begin = (c0 / DT_TK) * DT_TK;
   const int n_tiles = c1 > c0 ? (c1 - k_begin + DT_TK - 1) / DT_TK : 0;
 
+  // A thread's 16-byte pieces of a tile: piece n is row r0 + n * ROWS_STEP, chunk ch0.  The swizzle
+  // depends on the row only through its low three bits, which ROWS_STEP (a multiple of 8) leaves
+  // alone, so piece n lies a fixed distance behind piece 0 both in the cache and in shared memory.
+  constexpr int PIECES = DT_TK * CH / (DT_WARPS * 32), ROWS_STEP = DT_WARPS * 32 / CH;
+  static_assert(ROWS_STEP % 8 == 0 && PIECES * ROWS_STEP == DT_TK, "pieces of a tile");
+  const int r0 = tid / CH, ch0 = tid % CH;
+  const int sm_off0 = swz<HD>(r0, ch0), g_off0 = r0 * HD + ch0 * 8;
+
   auto load_tile = [&](int t, int buf) {
     const int kb = k_begin + t * DT_TK;
     const int page = pt[kb / page_size];
     const size_t base = (((size_t)(page < 0 ? 0 : page) * Hkv + kvh) * page_size + kb % page_size) * HD;
-    for (int i = tid; i < DT_TK * CH; i += DT_WARPS * 32) {
-      const int r = i / CH, ch = i % CH;
-      const bool valid = page >= 0 && kb + r < c1;
-      const size_t off = base + (size_t)(valid ? r : 0) * HD + ch * 8;
-      cp_async16(Ksm(buf) + swz<HD>(r, ch), k_cache + off, valid);
-      cp_async16(Vsm(buf) + swz<HD>(r, ch), v_cache + off, valid);
+    if (page >= 0 && kb + DT_TK <= c1) {     // a whole tile: nothing to test per piece
+      const bf16* kg = k_cache + base + g_off0;
+      const bf16* vg = v_cache + base + g_off0;
+      unsigned char* ks = Ksm(buf) + sm_off0;
+      unsigned char* vs = Vsm(buf) + sm_off0;
+#pragma unroll
+      for (int n = 0; n < PIECES; ++n) {
+        cp_async16(ks + n * ROWS_STEP * HD * 2, kg + n * ROWS_STEP * HD, true);
+        cp_async16(vs + n * ROWS_STEP * HD * 2, vg + n * ROWS_STEP * HD, true);
+      }
+    } else {
+      for (int i = tid; i < DT_TK * CH; i += DT_WARPS * 32) {
+        const int r = i / CH, ch = i % CH;
+        const bool valid = page >= 0 && kb + r < c1;
+        const size_t off = base + (size_t)(valid ? r : 0) * HD + ch * 8;
+        cp_async16(Ksm(buf) + swz<HD>(r, ch), k_cache + off, valid);
+        cp_async16(Vsm(buf) + swz<HD>(r, ch), v_cache + off, valid);
+      }
     }
     cp_async_commit();
   };
@@ -154,15 +174,21 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       }
     }
 
-    // scale, mask, online softmax; a row's 16 scores of this warp sit in the 4 lanes of a quad
+    // scale, mask, online softmax; a row's 16 scores of this warp sit in the 4 lanes of a quad.
+    // Only a chunk's first and last tile can hold keys outside [c0, c1).
+    const bool edge_tile = kb - 16 * warp < c0 || kb - 16 * warp + DT_TK > c1;   // the same for the whole block
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int kp = kb + 8 * j + 2 * c + (i & 1);
-        const bool vis = kp >= c0 && kp < c1;
-        s[j][i] = vis ? s[j][i] * scale : -INFINITY;
+        if (edge_tile) {
+          const int kp = kb + 8 * j + 2 * c + (i & 1);
+          const bool vis = kp >= c0 && kp < c1;
+          s[j][i] = vis ? s[j][i] * scale : -INFINITY;
+        } else {
+          s[j][i] *= scale;
+        }
         m_new[i >> 1] = fmaxf(m_new[i >> 1], s[j][i]);
       }
     float alpha[2], row_sum[2] = {0.f, 0.f};
@@ -188,12 +214,15 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       l_run[h] = l_run[h] * alpha[h] + row_sum[h];
       m_run[h] = m_new[h];
     }
+    // o * 1.0f is o: where no row of the warp found a new maximum the multiplications are left out
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-      o[j][0] *= alpha[0];
-      o[j][1] *= alpha[0];
-      o[j][2] *= alpha[1];
-      o[j][3] *= alpha[1];
+      for (int j = 0; j < HD / 8; ++j) {
+        o[j][0] *= alpha[0];
+        o[j][1] *= alpha[0];
+        o[j][2] *= alpha[1];
+        o[j][3] *= alpha[1];
+      }
     }
 
     // O += P V: one key step of 16, HD/8 column groups (two per ldmatrix)
