@@ -47,6 +47,12 @@ __device__ __forceinline__ void mma16816(float c[4], const unsigned a[4], unsign
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (x <= 0 here; -inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const unsigned*>(&t);
@@ -136,6 +142,9 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     cp_async_commit();
   };
 
+  // The softmax runs on base 2: scores are scaled by scale * log2(e) and the exponentials are ex2.approx
+  // (one instruction where expf is eight); the maxima go back to base e when they leave the loop.
+  const float scale2 = scale * 1.4426950408889634f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[HD / 8][4];
 #pragma unroll
@@ -185,9 +194,9 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
         if (edge_tile) {
           const int kp = kb + 8 * j + 2 * c + (i & 1);
           const bool vis = kp >= c0 && kp < c1;
-          s[j][i] = vis ? s[j][i] * scale : -INFINITY;
+          s[j][i] = vis ? s[j][i] * scale2 : -INFINITY;
         } else {
-          s[j][i] *= scale;
+          s[j][i] *= scale2;
         }
         m_new[i >> 1] = fmaxf(m_new[i >> 1], s[j][i]);
       }
@@ -196,14 +205,15 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     for (int h = 0; h < 2; ++h) {
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-      alpha[h] = m_new[h] == -INFINITY ? 1.f : expf(m_run[h] - m_new[h]);
+      alpha[h] = m_new[h] == -INFINITY ? 1.f : ex2(m_run[h] - m_new[h]);
     }
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int h = i >> 1;
-        const float p = s[j][i] == -INFINITY ? 0.f : expf(s[j][i] - m_new[h]);
+        // a masked score is -inf, and so is m_new while a row has seen masked keys only: only edge tiles
+        const float p = (edge_tile && s[j][i] == -INFINITY) ? 0.f : ex2(s[j][i] - m_new[h]);
         s[j][i] = p;
         row_sum[h] += p;
       }
@@ -251,7 +261,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   for (int h = 0; h < 2; ++h) {
     const int row = g + 8 * h;
     if (c == 0) {
-      sm_m[warp * 16 + row] = m_run[h];
+      sm_m[warp * 16 + row] = m_run[h] * 0.6931471805599453f;
       sm_l[warp * 16 + row] = l_run[h];
     }
 #pragma unroll
