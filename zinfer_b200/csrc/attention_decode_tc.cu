@@ -116,10 +116,19 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   const int r0 = tid / CH, ch0 = tid % CH;
   const int sm_off0 = swz<HD>(r0, ch0), g_off0 = r0 * HD + ch0 * 8;
 
-  auto load_tile = [&](int t, int buf) {
-    const int kb = k_begin + t * DT_TK;
-    const int page = pt[kb / page_size];
-    const size_t base = (((size_t)(page < 0 ? 0 : page) * Hkv + kvh) * page_size + kb % page_size) * HD;
+  // Tiles are loaded in order, so where the next one lies (entry of the page table, place in the page)
+  // is carried along: no division per tile.
+  int ld_kb = k_begin, ld_entry = k_begin / page_size, ld_in_page = k_begin % page_size;
+  auto load_tile = [&](int buf) {
+    const int kb = ld_kb;
+    const int page = pt[ld_entry];
+    const size_t base = (((size_t)(page < 0 ? 0 : page) * Hkv + kvh) * page_size + ld_in_page) * HD;
+    ld_kb += DT_TK;
+    ld_in_page += DT_TK;
+    if (ld_in_page == page_size) {
+      ld_in_page = 0;
+      ++ld_entry;
+    }
     if (page >= 0 && kb + DT_TK <= c1) {     // a whole tile: nothing to test per piece
       const bf16* kg = k_cache + base + g_off0;
       const bf16* vg = v_cache + base + g_off0;
@@ -156,12 +165,12 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   // iteration commits one group (an empty one when no tile is left), so "all but the newest
   // NST - 1 groups" is always "tile t has landed".
   for (int t = 0; t < NST - 1; ++t) {
-    if (t < n_tiles) load_tile(t, t);
+    if (t < n_tiles) load_tile(t);
     else cp_async_commit();
   }
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t % NST;
-    if (t + NST - 1 < n_tiles) load_tile(t + NST - 1, (t + NST - 1) % NST);
+    if (t + NST - 1 < n_tiles) load_tile((t + NST - 1) % NST);
     else cp_async_commit();
     cp_async_wait<NST - 1>();
     __syncthreads();
