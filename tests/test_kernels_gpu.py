@@ -56,12 +56,19 @@ def test_embed_and_status(k, dtype, dim):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,dim,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (2, 1000, 3e-6), (1, 16, 1e-5)])
+@pytest.mark.parametrize("n,dim,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (2, 1000, 3e-6), (1, 16, 1e-5),
+                                       (300, 2048, 1e-5), (261, 200, 1e-6), (257, 2052, 1e-5)])
 def test_rmsnorm(k, dtype, n, dim, eps):
+    """Few rows (a block per row) and 256 rows and more (a warp per row up to a width of 2048; the row
+    count no multiple of the 8 rows of a block)."""
     x = rnd((n, dim), 2, torch.float32, 3.0).cuda()
+    x[n // 2] *= 50.0                                   # rows of different sizes: a row's scale is its own
     w = (1 + rnd((dim,), 3, torch.float32, 0.1)).cuda()
     ref = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * w.double()
-    close(k.rmsnorm(x, w, eps, dtype), ref, dtype, "rmsnorm")
+    got = k.rmsnorm(x, w, eps, dtype)
+    for r in (0, n // 2, n - 1):
+        close(got[r], ref[r], dtype, f"rmsnorm row {r}")
+    close(got, ref, dtype, "rmsnorm")
     rows = torch.tensor([n - 1, 0], dtype=torch.int32).cuda()
     close(k.rmsnorm(x, w, eps, dtype, rows), ref[[n - 1, 0]], dtype, "rmsnorm rows")
 
