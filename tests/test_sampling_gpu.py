@@ -137,3 +137,26 @@ def test_xtc_removes_the_top_choices_but_the_last(k):
     kept = k.sample(torch.from_numpy(x).cuda(), torch.from_numpy(u).cuda(), temp=1.0, xtc_probability=0.5,
                     xtc_threshold=0.15, xtc_min_keep=V).cpu().numpy()
     assert {10, 3} & set(kept[100:].tolist()), "min_keep larger than what would stay: nothing is removed"
+
+
+def test_uniforms_made_on_the_device_are_the_hosts(k):
+    """Without uniforms the kernel computes them from (seed, request, the request's count of draws) as
+    sampling.sampler.uniform does on the host, and advances the count of every request it drew for:
+    the tokens equal those of the same rows with the host's uniforms, step after step, also when the
+    rows are a changing subset of the requests and the seed uses all 64 bits."""
+    from zinfer_b200.sampling.sampler import uniform
+    V, n_req = 5000, 7
+    seed = 0xF123456789ABCDEF
+    draws_dev = torch.zeros(n_req, dtype=torch.int32, device="cuda")
+    draws = [0] * n_req
+    opts = dict(temp=0.9, top_k=50, top_p=0.9, min_p=0.02, xtc_probability=0.5, xtc_threshold=0.05)
+    for step, rows in enumerate([[0, 1, 2, 3, 4, 5, 6], [6, 2, 4], [2], [0, 1, 2, 3, 4, 5, 6], [5, 0]]):
+        x = torch.from_numpy(logits_rows(len(rows), V, 100 + step)).cuda()
+        u = np.array([[uniform(seed, r, draws[r], 0), uniform(seed, r, draws[r], 1)] for r in rows], dtype=np.float32)
+        want = k.sample(x, torch.from_numpy(u).cuda(), **opts).cpu().tolist()
+        got = k.sample(x, None, seed=seed, req_ids=torch.tensor(rows, dtype=torch.int32).cuda(), draws=draws_dev,
+                       **opts).cpu().tolist()
+        assert got == want, f"step {step}: {got} != {want}"
+        for r in rows:
+            draws[r] += 1
+        assert draws_dev.cpu().tolist() == draws

@@ -313,13 +313,248 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
   }
 }
 
-// One draw per row.  uniforms[row] = {u for the draw, u for the XTC chance}, both in [0, 1).
+// The host's sampling.sampler.uniform(seed, request, draw, stream): a float32 in [0, 1) that is a
+// function of its four arguments only.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+__device__ __forceinline__ float counter_uniform(unsigned long long seed, int request, int draw, int stream) {
+  unsigned long long h = mix64(seed);
+  h = mix64(h ^ (unsigned long long)(unsigned)request);
+  h = mix64(h ^ (unsigned long long)(unsigned)draw);
+  h = mix64(h ^ (unsigned long long)stream);
+  return (float)(h >> 40) * (1.0f / 16777216.0f);
+}
+
+// ---------------------------------------------------------------------------------------
+// The chain on a short list.  When the filters can only keep tokens among the CAND_MAX best
+// (top-k of at most CAND_MAX; or top-p / min-p whose survivors are seen to lie among them),
+// the row is read twice (a histogram of the keys' upper 11 bits, then a gather of everything
+// at or above the bin in which the k-th best lies) and the rest of the chain runs on that list
+// in shared memory: the same prefixes, ties, predicates and index-order draw as the passes over
+// the whole row further down, at a tenth of their time.
+constexpr int CAND_MAX = 1024;
+constexpr int HIST_BITS = 11, HIST_BINS = 1 << HIST_BITS;
+
+struct Small {
+  float l[CAND_MAX];       // candidates in index order
+  int idx[CAND_MAX];
+  float l2[CAND_MAX];      // as gathered
+  int idx2[CAND_MAX];
+  float w[CAND_MAX];       // masses exp(l - mx), then weights exp((l - mx) / temp)
+  unsigned char in[CAND_MAX];
+  int hist[HIST_BINS];
+  int count, bin, above;
+};
+
+// Returns false, with nothing decided, if the list does not suffice; the caller then takes the
+// passes over the whole row.  k_eff: how many of the best the top-k stage keeps (V if it is off).
+__device__ bool sample_small(const float* row, int V, int k_eff, float temp, float top_p, float min_p,
+                             float xtc_probability, float xtc_threshold, int xtc_min_keep, float u_draw, float u_xtc,
+                             Shared& sh, Small& sm, int* picked_out) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int k_list = min(k_eff, CAND_MAX);           // the list holds the k_list best
+  // 1. histogram of the upper bits; equal bins of a warp are added as one
+  for (int b = tid; b < HIST_BINS; b += blockDim.x) sm.hist[b] = 0;
+  if (tid == 0) sm.count = 0;
+  __syncthreads();
+  // (sixteen loads under way per thread: one at a time, a pass over the row is its latency 64 times)
+  constexpr int UN = 16;
+  for (int base = 0; base < V; base += blockDim.x * UN) {
+    float v[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      v[u] = i < V ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u)
+      if (base + u * blockDim.x + tid < V) atomicAdd(&sm.hist[key_of(v[u]) >> (32 - HIST_BITS)], 1);
+  }
+  __syncthreads();
+  // 2. the bin of the k_list-th best: warp 0, lane j owns bins [HIST_BINS - 64 (j + 1), HIST_BINS - 64 j)
+  if (tid < 32) {
+    constexpr int PER = HIST_BINS / 32;
+    const int top = HIST_BINS - PER * lane;           // one past this lane's highest bin
+    int mine = 0;
+    for (int b = top - 1; b >= top - PER; --b) mine += sm.hist[b];
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    const int before = incl - mine;                    // elements in bins above this lane's
+    if (before < k_list && incl >= k_list) {           // exactly one lane (V >= k_list elements exist)
+      int acc = before, b = top - 1;
+      for (; b > top - PER; --b) {
+        if (acc + sm.hist[b] >= k_list) break;
+        acc += sm.hist[b];
+      }
+      sm.bin = b;
+      sm.above = acc;
+    }
+  }
+  __syncthreads();
+  const int bin0 = sm.bin;
+  const int n_c = sm.above + sm.hist[bin0];
+  if (n_c > CAND_MAX) return false;                    // too many values share the deciding bin
+  // 3. gather everything at or above that bin
+  for (int base = 0; base < V; base += blockDim.x * UN) {
+    float v[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      v[u] = i < V ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      if (i < V && (int)(key_of(v[u]) >> (32 - HIST_BITS)) >= bin0) {
+        const int pos = atomicAdd(&sm.count, 1);
+        sm.l2[pos] = v[u] == v[u] ? v[u] : -INFINITY;     // NaN read as -inf, as ld() does
+        sm.idx2[pos] = i;
+      }
+    }
+  }
+  __syncthreads();
+  // 4. into index order (the gather's order is whatever the atomics made it)
+  if (tid < n_c) {
+    const int my = sm.idx2[tid];
+    int rank = 0;
+    for (int j = 0; j < n_c; ++j) rank += sm.idx2[j] < my;
+    sm.l[rank] = sm.l2[tid];
+    sm.idx[rank] = my;
+  }
+  __syncthreads();
+  // 5. the k_list best of them: descending value, ties in index order
+  const bool have = tid < n_c;
+  const float my_l = have ? sm.l[tid] : -INFINITY;
+  const unsigned my_key = key_of(my_l);
+  int rank_desc = 0;
+  if (have)
+    for (int j = 0; j < n_c; ++j) {
+      const unsigned kj = key_of(sm.l[j]);
+      rank_desc += kj > my_key || (kj == my_key && j < tid);
+    }
+  bool member = have && rank_desc < k_list;
+  const float mx = block_reduce_max(member ? my_l : -INFINITY, sh);
+  const float e = member ? expf(my_l - mx) : 0.f;
+  auto minp_ok = [&](float l, float mass) { return min_p <= 0.f || l == mx || mass >= min_p; };
+  // 6. top-p: the shortest prefix of the descending order whose mass reaches top_p * total
+  sm.w[tid < CAND_MAX ? tid : 0] = 0.f;                 // (blockDim.x == CAND_MAX)
+  __syncthreads();
+  if (have) sm.w[tid] = e;
+  sm.in[tid] = member;
+  __syncthreads();
+  float total_e = block_reduce_sum(e, sh);               // a fixed order of additions: the same in every run
+  if (k_eff > k_list) {
+    // The list is a cut of a longer candidate set: the mass is the whole row's, and the list must be
+    // seen to hold every survivor (the prefix ends inside it, or its last member already fails min-p).
+    float all = 0.f;
+    for (int i = tid; i < V; i += blockDim.x) all += expf(ld(row, i) - mx);
+    all = block_reduce_sum(all, sh);
+    const bool prefix_inside = top_p < 1.0f && total_e >= top_p * all;
+    const float lowest = -block_reduce_max(member ? -my_l : -INFINITY, sh);
+    const bool minp_cuts = min_p > 0.f && !minp_ok(lowest, expf(lowest - mx));
+    if (!prefix_inside && !minp_cuts) return false;
+    total_e = all;
+  }
+  if (top_p < 1.0f) {
+    const float target = top_p * total_e;
+    float before = 0.f;
+    if (member)
+      for (int j = 0; j < n_c; ++j) {
+        const unsigned kj = key_of(sm.l[j]);
+        if (sm.in[j] && (kj > my_key || (kj == my_key && j < tid))) before += sm.w[j];
+      }
+    member = member && before < target;
+  }
+  const bool in_prefix = member;          // after top-k and top-p, before min-p
+  // 7. min-p on the value, temperature on the survivors
+  member = member && minp_ok(my_l, e);
+  const float inv_t = 1.0f / temp;
+  float wgt = member ? expf((my_l - mx) * inv_t) : 0.f;
+  __syncthreads();
+  sm.w[tid] = wgt;
+  sm.in[tid] = member;
+  __syncthreads();
+  float total = block_reduce_sum(wgt, sh);
+  const int n_keep = block_reduce_isum(member ? 1 : 0, sh);
+  // 8. XTC (src/sampler.zig:244-268): drop every survivor whose probability reaches the threshold
+  //    except the least probable of them
+  if (xtc_probability > 0.f && xtc_threshold <= 0.5f && n_keep >= 2 && total > 0.f && u_xtc <= xtc_probability) {
+    const float inv_tot = 1.0f / total;
+    const bool is_top = member && wgt * inv_tot >= xtc_threshold;
+    const int n_top = block_reduce_isum(is_top ? 1 : 0, sh);
+    const float min_l = -block_reduce_max(is_top ? -my_l : -INFINITY, sh);
+    const int pos_last = n_top > 0 ? n_top - 1 : 0;
+    if (pos_last > 0 && n_keep - pos_last >= max(1, xtc_min_keep)) {
+      // the last of the tops in the descending order: the lowest value, the highest index among its ties
+      const int last_idx = block_reduce_imax((in_prefix && my_l == min_l) ? sm.idx[tid] : -1, sh);
+      const unsigned xk = key_of(min_l);
+      const bool dropped = my_key > xk || (my_key == xk && have && sm.idx[tid] < last_idx);
+      if (dropped) {
+        member = false;
+        wgt = 0.f;
+      }
+      __syncthreads();
+      sm.w[tid] = wgt;
+      sm.in[tid] = member;
+      __syncthreads();
+      total = block_reduce_sum(wgt, sh);
+    }
+  }
+  // 9. the draw: first survivor, in index order, at which the running sum reaches u * total
+  const float r = u_draw * total;
+  float incl = 0.f;
+  if (have)
+    for (int j = 0; j <= tid; ++j) incl += sm.w[j];
+  const int picked = block_reduce_imin((member && incl >= r) ? sm.idx[tid] : 0x7fffffff, sh);
+  const int last_member = block_reduce_imax(member ? sm.idx[tid] : -1, sh);
+  *picked_out = picked != 0x7fffffff ? picked : max(last_member, 0);
+  return true;
+}
+
+// One draw per row.  Its two uniforms in [0, 1) (one for the draw, one for the XTC chance) are
+// uniforms[row] if given; else they are computed here from (seed, req_ids[row], draws[req_ids[row]]),
+// and that request's count of draws goes up by one: the host then has nothing to send per step.
 __global__ void __launch_bounds__(SAMP_THREADS)
     sample_kernel(const float* __restrict__ logits, int V, float temp, int top_k, float top_p, float min_p,
                   float xtc_probability, float xtc_threshold, int xtc_min_keep, const float* __restrict__ uniforms,
+                  unsigned long long seed, const int* __restrict__ req_ids, int* __restrict__ draws,
                   int* __restrict__ out) {
   __shared__ Shared sh;
+  __shared__ float s_u[2];
+  if (threadIdx.x == 0) {
+    if (uniforms) {
+      s_u[0] = uniforms[(size_t)blockIdx.x * 2];
+      s_u[1] = uniforms[(size_t)blockIdx.x * 2 + 1];
+    } else {
+      const int req = req_ids[blockIdx.x];
+      const int d = draws[req];
+      s_u[0] = counter_uniform(seed, req, d, 0);
+      s_u[1] = counter_uniform(seed, req, d, 1);
+      draws[req] = d + 1;
+    }
+  }
+  __syncthreads();
   const float* row = logits + (size_t)blockIdx.x * V;
+  {
+    __shared__ Small sm;
+    const int k_eff = (top_k > 0 && top_k < V) ? top_k : V;
+    int picked_small = 0;
+    if ((k_eff <= CAND_MAX || top_p < 1.0f || min_p > 0.f) &&
+        sample_small(row, V, k_eff, temp, top_p, min_p, xtc_probability, xtc_threshold, xtc_min_keep, s_u[0], s_u[1], sh,
+                     sm, &picked_small)) {
+      if (threadIdx.x == 0) out[blockIdx.x] = picked_small;
+      return;
+    }
+    __syncthreads();
+  }
   float mx = -INFINITY;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float v = row[i];
@@ -350,7 +585,7 @@ __global__ void __launch_bounds__(SAMP_THREADS)
   unsigned xtc_key = 0xffffffffu;  // survivors with key > xtc_key, or == and index < xtc_idx, are dropped
   int xtc_idx = -1;
   if (xtc_probability > 0.f && xtc_threshold <= 0.5f && n_keep >= 2 && total > 0.f &&
-      uniforms[(size_t)blockIdx.x * 2 + 1] <= xtc_probability) {
+      s_u[1] <= xtc_probability) {
     const float inv_tot = 1.0f / total;
     int n_top = 0;
     float min_l = INFINITY;
@@ -384,7 +619,7 @@ __global__ void __launch_bounds__(SAMP_THREADS)
   }
 
   // draw: first survivor, in index order, at which the running sum reaches u * total
-  const float r = uniforms[(size_t)blockIdx.x * 2] * total;
+  const float r = s_u[0] * total;
   float offset = 0.f;
   int last_member = -1, picked = 0x7fffffff;
   for (int base = 0; base < V; base += blockDim.x) {
@@ -432,13 +667,15 @@ int zk_argmax(const float* logits, int n, int V, int* out, int* feed, const int*
                              reinterpret_cast<unsigned*>(keys + n));
 }
 
+// uniforms [n, 2], or null and then seed, req_ids [n] (the request of each row; distinct) and
+// draws [requests] (how many draws each request has had; the kernel adds one for its rows).
 int zk_sample(const float* logits, int n, int V, float temp, int top_k, float top_p, float min_p,
-              float xtc_probability, float xtc_threshold, int xtc_min_keep, const float* uniforms, int* out,
-              cudaStream_t stream) {
+              float xtc_probability, float xtc_threshold, int xtc_min_keep, const float* uniforms,
+              long long seed, const int* req_ids, int* draws, int* out, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (V <= 0 || !(temp > 0.f) || top_k < 0 || !uniforms) return ZK_EINVAL;
+  if (V <= 0 || !(temp > 0.f) || top_k < 0 || (!uniforms && (!req_ids || !draws))) return ZK_EINVAL;
   sample_kernel<<<n, SAMP_THREADS, 0, stream>>>(logits, V, temp, top_k, top_p, min_p, xtc_probability, xtc_threshold,
-                                                xtc_min_keep, uniforms, out);
+                                                xtc_min_keep, uniforms, (unsigned long long)seed, req_ids, draws, out);
   return ZK_LAUNCH_STATUS();
 }
 

@@ -72,7 +72,7 @@ _SIGNATURES = {
     "sampling": {
         "zk_apply_penalties": "piipifppip",
         "zk_argmax": "piippppp",
-        "zk_sample": "piififfffippp",
+        "zk_sample": "piififfffip" + "lpp" + "pp",
     },
     "attention": {
         "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiipp",
@@ -783,16 +783,29 @@ def _argmax_scratch(device, n: int) -> torch.Tensor:
 
 
 def sample(logits, uniforms, temp: float, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
-           xtc_probability: float = 0.0, xtc_threshold: float = 0.1, xtc_min_keep: int = 1) -> torch.Tensor:
-    """One draw per row after top-k, top-p, min-p, temperature and XTC; uniforms [n, 2] in [0, 1)."""
+           xtc_probability: float = 0.0, xtc_threshold: float = 0.1, xtc_min_keep: int = 1, seed: int = 0,
+           req_ids: Optional[torch.Tensor] = None, draws: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One draw per row after top-k, top-p, min-p, temperature and XTC.  The row's two uniforms in
+    [0, 1) are uniforms[row] (float32 [n, 2]), or, with uniforms None, computed on the device as
+    sampling.sampler.uniform(seed, req_ids[row], draws[req_ids[row]], 0 and 1): req_ids int32 [n]
+    names each row's request (distinct), draws int32 [requests] counts each request's draws so far
+    and is advanced by one for the rows' requests."""
     _need(logits, "logits", torch.float32, (None, None))
     n, V = logits.shape
-    _need(uniforms, "uniforms", torch.float32, (n, 2))
+    if uniforms is not None:
+        _need(uniforms, "uniforms", torch.float32, (n, 2))
+    else:
+        _need(req_ids, "req_ids", torch.int32, (n,))
+        _need(draws, "draws", torch.int32, (None,))
     if not temp > 0:
         raise KernelError("sample: temperature must be positive (use argmax for greedy)")
     out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF          # the 64 bits as a signed value for the C side
+    if seed >= 1 << 63:
+        seed -= 1 << 64
     _check(_fn("sampling", "zk_sample")(_ptr(logits), n, V, temp, top_k, top_p, min_p, xtc_probability, xtc_threshold,
-                                        xtc_min_keep, _ptr(uniforms), _ptr(out), _stream()), "sample")
+                                        xtc_min_keep, _ptr(uniforms), seed, _ptr(req_ids),
+                                        _ptr(draws), _ptr(out), _stream()), "sample")
     return out
 
 

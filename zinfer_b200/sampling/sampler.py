@@ -133,6 +133,12 @@ class Sampler:
         self.history: list[list[int]] = [[] for _ in range(n_requests)]
         self.draws = [0] * n_requests
         self.breakers = tuple(breakers)
+        # the device's copy of `draws`, advanced by the sampling kernel itself, and the rows' request
+        # numbers as last sent: a step sends nothing unless the batch has changed
+        self._draws_dev: Optional[torch.Tensor] = None
+        self._rows: Optional[tuple] = None
+        self._rows_dev: Optional[torch.Tensor] = None
+        self._rows_pinned: Optional[torch.Tensor] = None
 
     @property
     def needs_history(self) -> bool:
@@ -178,10 +184,20 @@ class Sampler:
         self._penalties(logits, requests)
         if self.p.greedy:
             return kernels.argmax(logits)
-        u = np.empty((len(requests), 2), dtype=np.float32)
-        for i, r in enumerate(requests):
-            u[i, 0] = uniform(self.p.seed, r, self.draws[r], 0)
-            u[i, 1] = uniform(self.p.seed, r, self.draws[r], 1)
+        # The draw's uniforms are uniform(seed, request, draws[request], 0 and 1), computed by the kernel
+        # from its own count of the request's draws: nothing is copied to the device in a step whose
+        # rows are those of the step before, so the step can be queued behind the one that runs.
+        if self._draws_dev is None:
+            self._draws_dev = torch.zeros(len(self.draws), dtype=torch.int32, device=self.device)
+        rows = tuple(int(r) for r in requests)
+        if len(set(rows)) != len(rows):
+            raise ValueError("a request appears in two rows of one sampling step")
+        if rows != self._rows:
+            self._rows_pinned = torch.tensor(rows, dtype=torch.int32).pin_memory()
+            self._rows_dev = self._rows_pinned.to(self.device, non_blocking=True)
+            self._rows = rows
+        for r in rows:
             self.draws[r] += 1
-        return kernels.sample(logits, torch.from_numpy(u).to(self.device), self.p.temp, self.p.top_k, self.p.top_p,
-                              self.p.min_p, self.p.xtc_probability, self.p.xtc_threshold, self.p.xtc_min_keep)
+        return kernels.sample(logits, None, self.p.temp, self.p.top_k, self.p.top_p, self.p.min_p,
+                              self.p.xtc_probability, self.p.xtc_threshold, self.p.xtc_min_keep, seed=self.p.seed,
+                              req_ids=self._rows_dev, draws=self._draws_dev)
