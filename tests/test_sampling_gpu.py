@@ -160,3 +160,42 @@ def test_uniforms_made_on_the_device_are_the_hosts(k):
         for r in rows:
             draws[r] += 1
         assert draws_dev.cpu().tolist() == draws
+
+
+@pytest.mark.parametrize("opts", [dict(temp=1.0, top_p=0.9), dict(temp=0.7, min_p=0.02), dict(temp=1.2, top_p=0.8, min_p=0.01),
+                                  dict(temp=0.9, top_k=1024, top_p=0.95), dict(temp=0.9, top_k=1025, top_p=0.95),
+                                  dict(temp=1.0, top_k=3000)])
+@pytest.mark.parametrize("scale", [8.0, 1.0])
+def test_short_list_and_whole_row_give_the_plain_chain(k, opts, scale):
+    """Peaked rows (scale 8: the survivors of top-p and min-p lie among the 1,024 best, so the chain
+    runs on the short list) and flat rows (scale 1: they do not, and the passes over the whole row
+    take over), top-k at and beyond the list's length: the draws are the plain implementation's."""
+    n, V = 32, 65536
+    x = logits_rows(n, V, 77, scale)
+    x[3, 100] = np.nan
+    u = np.random.default_rng(5).random((n, 2)).astype(np.float32)
+    xs, us = torch.from_numpy(x).cuda(), torch.from_numpy(u).cuda()
+    got = k.sample(xs, us, **opts).cpu().numpy()
+    assert np.array_equal(got, k.sample(xs, us, **opts).cpu().numpy()), "two runs differ"
+    exact = 0
+    for i in range(n):
+        row = np.where(np.isnan(x[i]), -np.inf, x[i])
+        p = P.filtered_probs(row, opts["temp"], opts.get("top_k", 0), opts.get("top_p", 1.0), opts.get("min_p", 0.0))
+        assert p[got[i]] > 0, f"row {i}: token {got[i]} is outside the support"
+        exact += int(got[i] == expected_pick(p, float(u[i, 0])))
+    assert exact >= n - 1, f"only {exact} of {n} draws equal the plain implementation's"
+
+
+def test_more_ties_than_the_short_list_holds(k):
+    """2,000 tokens share the value at which top-k cuts: the deciding bin holds more than the short list
+    can, the passes over the whole row decide, and the cut still falls in index order."""
+    V = 6000
+    x = np.full((2, V), -3.0, dtype=np.float32)
+    x[:, 1000:3000] = 1.5
+    x[:, 4000] = 2.5
+    u = np.array([[0.9999, 0], [0.0, 0]], dtype=np.float32)
+    got = k.sample(torch.from_numpy(x).cuda(), torch.from_numpy(u).cuda(), temp=1.0, top_k=5).cpu().tolist()
+    assert got == [4000, 1000]          # the survivors are 4000 and 1000..1003; the draw walks them in index order
+    got = k.sample(torch.from_numpy(x).cuda(), torch.from_numpy(np.array([[0.5, 0], [0.7, 0]], dtype=np.float32)).cuda(),
+                   temp=1.0, top_k=5).cpu().tolist()
+    assert set(got) <= {1000, 1001, 1002, 1003, 4000}
