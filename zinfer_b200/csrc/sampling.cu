@@ -145,6 +145,46 @@ __device__ int nth_equal(const float* row, int V, unsigned T, int limit_cut, int
   return limit_cut;
 }
 
+// One pass of a radix selection over the whole row.  Four loads are under way per thread (one at a
+// time, a pass is the memory's latency V / threads times), and the lanes of a warp that hit the same
+// bin add to it as one: in the first pass nearly every element falls into two or three bins (the
+// upper bits of a float are its sign and exponent), and 65,536 atomic adds to three shared-memory
+// words, the 64-bit ones by compare-and-swap, took a millisecond.
+// f(i, l, &bin, &mass) says whether element i takes part, in which bin, with what mass.
+template <typename F>
+__device__ __forceinline__ void radix_pass(const float* row, int V, Shared& sh, bool with_mass, F f) {
+  constexpr int UN = 4;
+  const int lane = threadIdx.x & 31;
+  for (int base = 0; base < V; base += blockDim.x * UN) {
+    float v[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      v[u] = i < V ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      unsigned bin = 0xffffffffu;
+      unsigned long long mass = 0ull;
+      const bool act = i < V && f(i, v[u] == v[u] ? v[u] : -INFINITY, &bin, &mass);
+      if (!__any_sync(0xffffffffu, act)) continue;
+      const unsigned peers = __match_any_sync(0xffffffffu, act ? bin : 0xffffffffu);
+      if (act) {
+        unsigned lo = 0, hi = 0;
+        if (with_mass) {     // a mass has at most 41 bits: two sums of 32 lanes' halves fit 32 bits each
+          lo = __reduce_add_sync(peers, (unsigned)(mass & 0xFFFFFull));
+          hi = __reduce_add_sync(peers, (unsigned)(mass >> 20));
+        }
+        if (lane == __ffs(peers) - 1) {
+          atomicAdd(&sh.ibins[bin], __popc(peers));
+          if (with_mass) atomicAdd(&sh.mbins[bin], ((unsigned long long)hi << 20) + lo);
+        }
+      }
+    }
+  }
+}
+
 // Top-k prefix by counting radix selection.
 __device__ Prefix select_top_k(const float* row, int V, int k, Shared& sh) {
   unsigned prefix = 0, mask = 0;
@@ -152,10 +192,11 @@ __device__ Prefix select_top_k(const float* row, int V, int k, Shared& sh) {
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int b = threadIdx.x; b < 256; b += blockDim.x) sh.ibins[b] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const unsigned key = key_of(ld(row, i));
-      if ((key & mask) == prefix) atomicAdd(&sh.ibins[(key >> shift) & 255], 1);
-    }
+    radix_pass(row, V, sh, false, [&](int, float l, unsigned* bin, unsigned long long*) {
+      const unsigned key = key_of(l);
+      *bin = (key >> shift) & 255;
+      return (key & mask) == prefix;
+    });
     __syncthreads();
     if (threadIdx.x == 0) {
       int acc = 0, b = 255;
@@ -196,14 +237,13 @@ __device__ Prefix select_top_p(const float* row, int V, const Prefix& in, float 
       sh.mbins[b] = 0ull;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float l = ld(row, i);
+    radix_pass(row, V, sh, true, [&](int i, float l, unsigned* bin, unsigned long long* mass) {
       const unsigned key = key_of(l);
-      if ((key & mask) == prefix && in.has(key, i)) {
-        atomicAdd(&sh.ibins[(key >> shift) & 255], 1);
-        atomicAdd(&sh.mbins[(key >> shift) & 255], (unsigned long long)(expf(l - mx) * MASS_UNIT));
-      }
-    }
+      if ((key & mask) != prefix || !in.has(key, i)) return false;
+      *bin = (key >> shift) & 255;
+      *mass = (unsigned long long)(expf(l - mx) * MASS_UNIT);
+      return true;
+    });
     __syncthreads();
     if (threadIdx.x == 0) {
       float acc = 0.f;
@@ -618,30 +658,76 @@ __global__ void __launch_bounds__(SAMP_THREADS)
     }
   }
 
-  // draw: first survivor, in index order, at which the running sum reaches u * total
+  // draw: first survivor, in index order, at which the running sum reaches u * total.  Every warp owns
+  // a stretch of the row: the warps' sums say in which stretch the sum reaches the target, and only
+  // that warp walks its stretch a second time, scanning 32 weights at a step.
   const float r = s_u[0] * total;
-  float offset = 0.f;
-  int last_member = -1, picked = 0x7fffffff;
-  for (int base = 0; base < V; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    float w = 0.f;
-    bool member = false;
-    if (i < V) {
-      const float l = ld(row, i);
-      const unsigned key = key_of(l);
-      const bool dropped = key > xtc_key || (key == xtc_key && i < xtc_idx);
-      member = !dropped && keep.has(key, i) && (min_p <= 0.f || l == mx || expf(l - mx) >= min_p);
-      if (member) w = expf((l - mx) * inv_t);
+  auto weight_of = [&](int i, float v, bool* member) {
+    const float l = v == v ? v : -INFINITY;
+    const unsigned key = key_of(l);
+    const bool dropped = key > xtc_key || (key == xtc_key && i < xtc_idx);
+    *member = !dropped && keep.has(key, i) && (min_p <= 0.f || l == mx || expf(l - mx) >= min_p);
+    return *member ? expf((l - mx) * inv_t) : 0.f;
+  };
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int stretch = ((V + n_warps - 1) / n_warps + 31) / 32 * 32;
+  const int lo = min(V, warp * stretch), hi = min(V, lo + stretch);
+  constexpr int UN = 8;
+  float wsum = 0.f;
+  int wlast = -1;
+  for (int base = lo; base < hi; base += 32 * UN) {
+    float v[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + 32 * u + lane;
+      v[u] = i < hi ? row[i] : 0.f;
     }
-    float chunk_total;
-    const float incl = block_scan_incl(w, sh, &chunk_total);
-    const int hit = (member && offset + incl >= r) ? i : 0x7fffffff;
-    picked = block_reduce_imin(hit, sh);
-    last_member = max(last_member, block_reduce_imax(member ? i : -1, sh));
-    if (picked != 0x7fffffff) break;
-    offset += chunk_total;
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int i = base + 32 * u + lane;
+      bool member = false;
+      if (i < hi) wsum += weight_of(i, v[u], &member);
+      if (member) wlast = i;
+    }
   }
-  if (threadIdx.x == 0) out[blockIdx.x] = picked != 0x7fffffff ? picked : max(last_member, 0);
+  wsum = warp_sum(wsum);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wlast = max(wlast, __shfl_xor_sync(0xffffffffu, wlast, o));
+  __syncthreads();
+  if (lane == 0) {
+    sh.fred[warp] = wsum;
+    sh.ired[warp] = wlast;
+  }
+  __syncthreads();
+  float offset = 0.f;          // weight before this warp's stretch, added in warp order by every thread alike
+  int target_warp = -1, last_member = -1;
+  for (int w = 0; w < n_warps; ++w) {
+    if (target_warp < 0 && sh.ired[w] >= 0 && offset + sh.fred[w] >= r) target_warp = w;
+    if (target_warp < 0) offset += sh.fred[w];
+    last_member = max(last_member, sh.ired[w]);
+  }
+  if (target_warp < 0) {        // rounding left the target a hair above the whole sum
+    if (threadIdx.x == 0) out[blockIdx.x] = max(last_member, 0);
+    return;
+  }
+  if (warp == target_warp) {
+    int picked = -1;
+    for (int base = lo; base < hi && picked < 0; base += 32) {
+      const int i = base + lane;
+      bool member = false;
+      float w = i < hi ? weight_of(i, row[i], &member) : 0.f;
+      float incl = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float nb = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += nb;
+      }
+      const unsigned hits = __ballot_sync(0xffffffffu, member && offset + incl >= r);
+      if (hits) picked = base + __ffs(hits) - 1;
+      offset += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) out[blockIdx.x] = picked >= 0 ? picked : wlast;   // wlast: the stretch's last survivor
+  }
 }
 
 extern "C" {
