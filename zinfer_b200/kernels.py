@@ -144,7 +144,15 @@ def sm_count(device=None) -> int:
     return n
 
 
+# The current stream's handle, asked for at every launch.  torch.cuda.current_stream() builds a Stream
+# object each time (some 5 us, a fifth of the host's time per launch of an unrecorded step); the
+# raw getter behind it returns the handle itself.  Where a torch build lacks it the public call does.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
