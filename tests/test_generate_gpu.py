@@ -216,3 +216,36 @@ def test_running_one_step_ahead_changes_no_token(model_folders, temp):
     assert any(r.finish_reason == "stop" for r in b) and any(r.finish_reason != "stop" for r in b)
     plain.cache.check_consistency()
     ahead.cache.check_consistency()
+
+
+@pytest.mark.parametrize("temp", [0.0, 0.8])
+def test_repetition_penalty_through_the_entry_point(model_folders, temp):
+    """With a repetition penalty the loop runs a step ahead too (the window of recent tokens lives on
+    the device).  Greedy: every token is the arg-max of the plain logits after the plain penalty over
+    the last 64 tokens of prompt and output, for prompts shorter and longer than the window.  Sampled:
+    the tokens are those of the loop that does not run ahead."""
+    import zinfer_b200 as z
+    import plain_lfm2 as P
+    folder = model_folders["tiny_b"]
+    plain = PlainLfm2(folder, dtype=np.float64)
+    vocab = plain.cfg["vocab_size"]
+    prompts = [helpers.random_tokens(900 + i, n, vocab) for i, n in enumerate([3, 80, 17, 1, 64])]
+    model = z.load(folder, dtype="float32")
+    ahead = z.Engine(model, max_batch=3, max_seq_len=256, page_size=16)
+    out = ahead.generate(prompts, max_new_tokens=20, temp=temp, top_k=0, top_p=1.0, min_p=0.0, seed=2,
+                         repeat_penalty=1.7, stop_ids=[])
+    if temp == 0.0:
+        for p, r in zip(prompts, out):
+            toks = list(p)
+            for i, t in enumerate(r.tokens):
+                row = P.repeat_penalty(plain.logits(toks)[-1], toks, 1.7)
+                assert t == int(np.argmax(row)), f"token {i}: {t}, plain {int(np.argmax(row))}"
+                toks.append(t)
+        # the penalty changes what is generated (else the test would not see a missing one)
+        free = ahead.generate(prompts, max_new_tokens=20, temp=0.0, stop_ids=[])
+        assert any(a.tokens != b.tokens for a, b in zip(out, free))
+    else:
+        slow = z.Engine(model, max_batch=3, max_seq_len=256, page_size=16, lookahead=False)
+        ref = slow.generate(prompts, max_new_tokens=20, temp=temp, top_k=0, top_p=1.0, min_p=0.0, seed=2,
+                            repeat_penalty=1.7, stop_ids=[])
+        assert [r.tokens for r in out] == [r.tokens for r in ref]

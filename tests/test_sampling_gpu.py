@@ -199,3 +199,29 @@ def test_more_ties_than_the_short_list_holds(k):
     got = k.sample(torch.from_numpy(x).cuda(), torch.from_numpy(np.array([[0.5, 0], [0.7, 0]], dtype=np.float32)).cuda(),
                    temp=1.0, top_k=5).cpu().tolist()
     assert set(got) <= {1000, 1001, 1002, 1003, 4000}
+
+
+def test_repetition_penalty_from_the_window_on_the_device(k):
+    """The device keeps each request's last 64 tokens as a ring: tokens appended one by one (more than
+    64 of them, with repeats) and the penalty read from the ring equal the plain implementation's
+    penalty on the host's history, for rows that are a changing subset of the requests."""
+    W = k.recent_window()
+    V, n_req = 500, 4
+    rng = np.random.default_rng(9)
+    recent = torch.full((n_req, W), -1, dtype=torch.int32, device="cuda")
+    seen = torch.zeros(n_req, dtype=torch.int32, device="cuda")
+    hist = [[] for _ in range(n_req)]
+    for step in range(150):
+        rows = sorted(rng.choice(n_req, size=rng.integers(1, n_req + 1), replace=False).tolist())
+        toks = rng.integers(0, 40, size=len(rows)).astype(np.int32)          # few values: many repeats
+        req = torch.tensor(rows, dtype=torch.int32).cuda()
+        if step % 10 == 9:
+            x = logits_rows(len(rows), V, 300 + step)
+            dev = torch.from_numpy(x).cuda()
+            k.penalize_recent(dev, recent, seen, req, 1.3)
+            want = np.stack([P.repeat_penalty(x[i], hist[r], 1.3) if hist[r] else x[i] for i, r in enumerate(rows)])
+            assert np.array_equal(dev.cpu().numpy(), want), f"step {step}"
+        k.recent_append(torch.from_numpy(toks).cuda(), recent, seen, req)
+        for r, t in zip(rows, toks.tolist()):
+            hist[r].append(t)
+    assert seen.cpu().tolist() == [len(h) for h in hist] and max(len(h) for h in hist) > W

@@ -730,6 +730,41 @@ __global__ void __launch_bounds__(SAMP_THREADS)
   }
 }
 
+// The repetition penalty from a window kept on the device: recent [requests, RECENT_N] holds each
+// request's last tokens as a ring, seen [requests] how many it has had in all.  One warp per row
+// penalises every distinct token among the last min(seen, RECENT_N) once (src/sampler.zig:91-100).
+constexpr int RECENT_N = 64;
+
+__global__ void penalize_recent_kernel(float* __restrict__ logits, int V, const int* __restrict__ recent,
+                                       const int* __restrict__ seen, const int* __restrict__ req_ids, float penalty) {
+  __shared__ int win[RECENT_N];
+  const int req = req_ids[blockIdx.x];
+  const int n = min(seen[req], RECENT_N);
+  for (int j = threadIdx.x; j < RECENT_N; j += blockDim.x) win[j] = j < n ? recent[(size_t)req * RECENT_N + j] : -1;
+  __syncthreads();
+  float* row = logits + (size_t)blockIdx.x * V;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const int tok = win[j];
+    bool first = tok >= 0 && tok < V;
+    for (int i = 0; i < j && first; ++i) first = win[i] != tok;
+    if (first) {
+      const float l = row[tok];
+      row[tok] = l > 0.f ? l / penalty : l * penalty;
+    }
+  }
+}
+
+// tokens [n] (what the rows just sampled) go into their requests' rings.
+__global__ void recent_append_kernel(const int* __restrict__ tokens, int n, int* __restrict__ recent,
+                                     int* __restrict__ seen, const int* __restrict__ req_ids) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  const int req = req_ids[r];
+  const int s = seen[req];
+  recent[(size_t)req * RECENT_N + s % RECENT_N] = tokens[r];
+  seen[req] = s + 1;
+}
+
 extern "C" {
 
 int zk_apply_penalties(float* logits, int n, int V, const int* rep_tokens, int R, float rep_penalty,
@@ -737,6 +772,24 @@ int zk_apply_penalties(float* logits, int n, int V, const int* rep_tokens, int R
   if (n <= 0) return 0;
   if (V <= 0 || R < 0 || P < 0) return ZK_EINVAL;
   penalties_kernel<<<n, 128, 0, stream>>>(logits, V, rep_tokens, R, rep_penalty, dry_tokens, dry_pen, P);
+  return ZK_LAUNCH_STATUS();
+}
+
+int zk_recent_window() { return RECENT_N; }
+
+// logits [n, V] edited in place from the device's windows; req_ids [n] names each row's request.
+int zk_penalize_recent(float* logits, int n, int V, const int* recent, const int* seen, const int* req_ids,
+                       float penalty, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (V <= 0 || !recent || !seen || !req_ids || !(penalty > 0.f)) return ZK_EINVAL;
+  penalize_recent_kernel<<<n, 64, 0, stream>>>(logits, V, recent, seen, req_ids, penalty);
+  return ZK_LAUNCH_STATUS();
+}
+
+int zk_recent_append(const int* tokens, int n, int* recent, int* seen, const int* req_ids, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!tokens || !recent || !seen || !req_ids) return ZK_EINVAL;
+  recent_append_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, n, recent, seen, req_ids);
   return ZK_LAUNCH_STATUS();
 }
 

@@ -194,7 +194,7 @@ class GenerationLoop:
         must not need the host's history of a request."""
         pending, keep = None, None       # the copy of `toks_dev` under way, and which of its rows are `active`
         # a backend whose steps end with the arg-max of their logits spares a greedy sampler its kernel
-        greedy = getattr(be, "greedy_tokens", None) if getattr(getattr(sampler, "p", None), "greedy", False) else None
+        greedy = getattr(be, "greedy_tokens", None) if getattr(sampler, "plain_greedy", False) else None
         while True:
             # Requests that go on unless the token they are about to receive is a stop token.
             # Their step is launched now, on the device's copy of those tokens; the host reads

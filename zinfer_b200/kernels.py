@@ -71,6 +71,9 @@ _SIGNATURES = {
     },
     "sampling": {
         "zk_apply_penalties": "piipifppip",
+        "zk_recent_window": "",
+        "zk_penalize_recent": "piipppfp",
+        "zk_recent_append": "pipppp",
         "zk_argmax": "piippppp",
         "zk_sample": "piififfffip" + "lpp" + "pp",
     },
@@ -757,6 +760,35 @@ def apply_penalties(logits, rep_tokens, rep_penalty: float, dry_tokens, dry_pen)
         _need(dry_pen, "dry_pen", torch.float32, (n, P))
     _check(_fn("sampling", "zk_apply_penalties")(_ptr(logits), n, V, _ptr(rep_tokens), R, rep_penalty,
                                                  _ptr(dry_tokens), _ptr(dry_pen), P, _stream()), "apply_penalties")
+
+
+def recent_window() -> int:
+    """How many of a request's last tokens the device's window for the repetition penalty holds."""
+    return _fn("sampling", "zk_recent_window")()
+
+
+def penalize_recent(logits, recent, seen, req_ids, penalty: float) -> None:
+    """In place: the repetition penalty (l > 0 ? l / F : l * F) on every distinct token among the last
+    tokens of each row's request.  recent int32 [requests, recent_window()] is a ring per request,
+    seen int32 [requests] how many tokens each has had, req_ids int32 [n] the request of each row."""
+    _need(logits, "logits", torch.float32, (None, None))
+    n, V = logits.shape
+    _need(recent, "recent", torch.int32, (None, recent_window()))
+    _need(seen, "seen", torch.int32, (recent.shape[0],))
+    _need(req_ids, "req_ids", torch.int32, (n,))
+    _check(_fn("sampling", "zk_penalize_recent")(_ptr(logits), n, V, _ptr(recent), _ptr(seen), _ptr(req_ids),
+                                                 float(penalty), _stream()), "penalize_recent")
+
+
+def recent_append(tokens, recent, seen, req_ids) -> None:
+    """tokens int32 [n], one per row, enter their requests' rings (see penalize_recent)."""
+    n = tokens.shape[0]
+    _need(tokens, "tokens", torch.int32, (n,))
+    _need(recent, "recent", torch.int32, (None, recent_window()))
+    _need(seen, "seen", torch.int32, (recent.shape[0],))
+    _need(req_ids, "req_ids", torch.int32, (n,))
+    _check(_fn("sampling", "zk_recent_append")(_ptr(tokens), n, _ptr(recent), _ptr(seen), _ptr(req_ids), _stream()),
+           "recent_append")
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed: Optional[torch.Tensor] = None,

@@ -3,10 +3,12 @@
 Names, meanings and defaults of the options are the reference's `Params`
 (src/sampler.zig:3-27): temp (<= 0 is greedy), top_k (0 = off), top_p, min_p, repeat_penalty
 over the last 64 tokens (1 = off), DRY and XTC options, seed.  The filter chain and the draw run
-on the device (csrc/sampling.cu); the host only decides WHICH tokens the sparse penalties touch:
-the distinct tokens among the last 64 (src/sampler.zig:91-100) and the DRY continuation tokens
-with their penalties, found with the Z-algorithm on the reversed history
-(src/sampler.zig:104-187).
+on the device (csrc/sampling.cu); the host decides WHICH tokens the DRY penalty touches (the continuation
+tokens with their penalties, found with the Z-algorithm on the reversed history,
+src/sampler.zig:104-187), and with DRY on also lists the distinct tokens among the last 64 for
+the repetition penalty (src/sampler.zig:91-100).  The repetition penalty alone works from a window
+of each request's last 64 tokens kept on the device: the prompt's end is sent once, every sampled
+token is appended by a kernel, and the host has nothing to send or to wait for in a step.
 
 Random numbers are counter based: the uniforms of a draw depend only on (seed, request index,
 number of tokens the request has sampled so far), never on which other requests share the batch.
@@ -139,13 +141,27 @@ class Sampler:
         self._rows: Optional[tuple] = None
         self._rows_dev: Optional[torch.Tensor] = None
         self._rows_pinned: Optional[torch.Tensor] = None
+        # the device's window of each request's last tokens (a ring) for the repetition penalty, how
+        # many tokens each request has had, and which requests' prompts have been sent
+        self._recent: Optional[torch.Tensor] = None
+        self._seen: Optional[torch.Tensor] = None
+        self._sent = [False] * n_requests
 
     @property
     def needs_history(self) -> bool:
-        """Whether sampling a request's next token needs its earlier tokens on the host (the
-        repetition and DRY penalties do); if not, a step may be launched before the host has read
-        the previous step's tokens."""
-        return self.p.repeat_penalty != 1.0 or self.p.dry_multiplier != 0.0
+        """Whether sampling a request's next token needs its earlier tokens on the host (the DRY
+        penalty does); if not, a step may be launched before the host has read the previous
+        step's tokens."""
+        return self.p.dry_multiplier != 0.0
+
+    @property
+    def plain_greedy(self) -> bool:
+        """Greedy with no penalty: the token is the arg-max of the logits as the model left them."""
+        return self.p.greedy and self.p.repeat_penalty == 1.0 and self.p.dry_multiplier == 0.0
+
+    @property
+    def _window_on_device(self) -> bool:
+        return self.p.repeat_penalty != 1.0 and self.p.dry_multiplier == 0.0
 
     def accept(self, request: int, tokens: Sequence[int]) -> None:
         """Records tokens that entered the context, prompt or generated (src/sampler.zig:84-89)."""
@@ -178,17 +194,8 @@ class Sampler:
             dry_t, dry_p = torch.from_numpy(t).to(self.device), torch.from_numpy(v).to(self.device)
         kernels.apply_penalties(logits, rep, p.repeat_penalty, dry_t, dry_p)
 
-    def sample(self, logits: torch.Tensor, requests: Sequence[int]) -> torch.Tensor:
-        """One token per row of float32 logits [n, V] (row i belongs to requests[i]); int32 on the
-        device.  `logits` is edited in place by the penalties, as in the reference."""
-        self._penalties(logits, requests)
-        if self.p.greedy:
-            return kernels.argmax(logits)
-        # The draw's uniforms are uniform(seed, request, draws[request], 0 and 1), computed by the kernel
-        # from its own count of the request's draws: nothing is copied to the device in a step whose
-        # rows are those of the step before, so the step can be queued behind the one that runs.
-        if self._draws_dev is None:
-            self._draws_dev = torch.zeros(len(self.draws), dtype=torch.int32, device=self.device)
+    def _rows_on_device(self, requests: Sequence[int]) -> torch.Tensor:
+        """The rows' request numbers as an int32 tensor; sent only when the batch has changed."""
         rows = tuple(int(r) for r in requests)
         if len(set(rows)) != len(rows):
             raise ValueError("a request appears in two rows of one sampling step")
@@ -196,8 +203,53 @@ class Sampler:
             self._rows_pinned = torch.tensor(rows, dtype=torch.int32).pin_memory()
             self._rows_dev = self._rows_pinned.to(self.device, non_blocking=True)
             self._rows = rows
-        for r in rows:
-            self.draws[r] += 1
-        return kernels.sample(logits, None, self.p.temp, self.p.top_k, self.p.top_p, self.p.min_p,
-                              self.p.xtc_probability, self.p.xtc_threshold, self.p.xtc_min_keep, seed=self.p.seed,
-                              req_ids=self._rows_dev, draws=self._draws_dev)
+        return self._rows_dev
+
+    def _send_windows(self, requests: Sequence[int]) -> None:
+        """The end of the history (the prompt) of every request that samples for the first time."""
+        n_win = kernels.recent_window()
+        if self._recent is None:
+            self._recent = torch.full((len(self.history), n_win), -1, dtype=torch.int32, device=self.device)
+            self._seen = torch.zeros(len(self.history), dtype=torch.int32, device=self.device)
+        new = [r for r in requests if not self._sent[r]]
+        if not new:
+            return
+        win = np.full((len(new), n_win), -1, dtype=np.int32)
+        cnt = np.zeros(len(new), dtype=np.int32)
+        for i, r in enumerate(new):
+            tail = self.history[r][-n_win:]
+            win[i, :len(tail)] = tail
+            cnt[i] = len(tail)
+            self._sent[r] = True
+        where = torch.tensor(new, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+        self._recent.index_copy_(0, where, torch.from_numpy(win).pin_memory().to(self.device, non_blocking=True))
+        self._seen.index_copy_(0, where, torch.from_numpy(cnt).pin_memory().to(self.device, non_blocking=True))
+
+    def sample(self, logits: torch.Tensor, requests: Sequence[int]) -> torch.Tensor:
+        """One token per row of float32 logits [n, V] (row i belongs to requests[i]); int32 on the
+        device.  `logits` is edited in place by the penalties, as in the reference."""
+        rows_dev = None
+        if self._window_on_device:
+            rows_dev = self._rows_on_device(requests)
+            self._send_windows(requests)
+            kernels.penalize_recent(logits, self._recent, self._seen, rows_dev, self.p.repeat_penalty)
+        else:
+            self._penalties(logits, requests)
+        if self.p.greedy:
+            tokens = kernels.argmax(logits)
+        else:
+            # The draw's uniforms are uniform(seed, request, draws[request], 0 and 1), computed by the
+            # kernel from its own count of the request's draws: nothing is copied to the device in a
+            # step whose rows are those of the step before, so the step can be queued behind the one
+            # that runs.
+            if self._draws_dev is None:
+                self._draws_dev = torch.zeros(len(self.draws), dtype=torch.int32, device=self.device)
+            rows_dev = self._rows_on_device(requests)
+            for r in requests:
+                self.draws[r] += 1
+            tokens = kernels.sample(logits, None, self.p.temp, self.p.top_k, self.p.top_p, self.p.min_p,
+                                    self.p.xtc_probability, self.p.xtc_threshold, self.p.xtc_min_keep, seed=self.p.seed,
+                                    req_ids=rows_dev, draws=self._draws_dev)
+        if self._window_on_device:
+            kernels.recent_append(tokens, self._recent, self._seen, rows_dev)
+        return tokens
