@@ -8,6 +8,7 @@ these functions: without a CUDA device, a compiler or a loadable library they ra
 from __future__ import annotations
 
 import ctypes
+import functools
 from typing import Optional
 
 import torch
@@ -350,13 +351,23 @@ def gemm_tc_force_form(form: int) -> None:
     _check(_fn("gemm_tc", "zk_gemm_tc_force_form")(int(form)), "gemm_tc_force_form")
 
 
+_constants: dict[str, int] = {}     # what the libraries say about themselves, asked once
+
+
+def _constant(lib_name: str, fn_name: str) -> int:
+    v = _constants.get(fn_name)
+    if v is None:
+        v = _constants[fn_name] = _fn(lib_name, fn_name)()
+    return v
+
+
 def gemm_skinny_max_m() -> int:
-    return _fn("gemm_skinny", "zk_gemm_skinny_max_m")()
+    return _constant("gemm_skinny", "zk_gemm_skinny_max_m")
 
 
 def gemm_skinny_fused_max_m() -> int:
     """Most rows for which the skinny kernels fuse RMSNorm, SwiGLU or the short convolution."""
-    return _fn("gemm_skinny", "zk_gemm_skinny_fused_max_m")()
+    return _constant("gemm_skinny", "zk_gemm_skinny_fused_max_m")
 
 
 class NormInput:
@@ -571,11 +582,11 @@ def conv_decode(bcx, state, w, bias, seq_slot, interleave: int = 0) -> torch.Ten
 # ------------------------------------------------------------------------------- attention
 
 def attn_rows_per_block() -> int:
-    return _fn("attention", "zk_attn_rows_per_block")()
+    return _constant("attention", "zk_attn_rows_per_block")
 
 
 def attn_max_head_dim() -> int:
-    return _fn("attention", "zk_attn_max_head_dim")()
+    return _constant("attention", "zk_attn_max_head_dim")
 
 
 def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, n_heads: int,
@@ -648,6 +659,7 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
     return _may_take(lib, n_heads, n_kv, head_dim, page_size) and bool(_fn(lib, fn)(n_heads, n_kv, head_dim, page_size))
 
 
+@functools.lru_cache(maxsize=None)      # a pure function of sizes, asked for by every attention layer of every step
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool, window: int = 0) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
@@ -764,7 +776,7 @@ def apply_penalties(logits, rep_tokens, rep_penalty: float, dry_tokens, dry_pen)
 
 def recent_window() -> int:
     """How many of a request's last tokens the device's window for the repetition penalty holds."""
-    return _fn("sampling", "zk_recent_window")()
+    return _constant("sampling", "zk_recent_window")
 
 
 def penalize_recent(logits, recent, seen, req_ids, penalty: float) -> None:
