@@ -17,6 +17,10 @@
 //            partial tile in its own shared memory, and after a cluster barrier every block adds
 //            the partials of its share of the tokens in split order, reading the other blocks'
 //            shared memory directly (no workspace, no atomics, the same bits each run).
+//            Its epilogues also take part in the RMSNorm around them: a product whose input rows
+//            came as bfloat16(x * norm weight) with partial sums of x^2 scales token t's sums by
+//            1 / sqrt(sum / K + eps), and a product that sums into the float32 residual rows can
+//            write those two things for the norm that reads the rows next.
 // Products of more than 64 rows with N a multiple of 256 take the persistent form further down
 // (one block, or a pair of blocks with tcgen05.mma.cta_group::2, per SM walking 256-wide tiles, a
 // TMA-store epilogue).  Every kernel here is launched as a dependent launch: the producer requests
