@@ -210,7 +210,8 @@ def test_gemm_skinny_with_fused_norm(k, M, N, K):
     assert not k.gemm_skinny_takes(k.NormInput(rnd((17, K), 1, torch.float32).cuda(), nw, 1e-5), w)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (8, 2048, 8192), (5, 5000, 64), (8, 16 * 148 * 6 + 24, 32), (3, 16, 8)])
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (8, 2048, 8192), (5, 5000, 64), (8, 16 * 148 * 6 + 24, 32), (3, 16, 8),
+                                   (9, 331, 80), (16, 2048, 8192), (13, 5000, 64), (16, 16 * 148 * 6 + 24, 32)])
 def test_gemm_skinny_writes_the_next_norms_inputs(k, M, N, K):
     """The accumulating contraction into float32 rows also writes bfloat16(rows * norm weight) and the
     rows' sums of squares per 16 columns: all three kernel shapes (few, some, many blocks), a ragged
@@ -231,7 +232,7 @@ def test_gemm_skinny_writes_the_next_norms_inputs(k, M, N, K):
     sq[:, :N] = res.double() ** 2
     close(emit.ssq, sq.reshape(M, -1, 16).sum(-1), torch.float32, "sums of squares per 16 columns")
     with pytest.raises(k.KernelError):
-        k.gemm_skinny(rnd((9, K), 1, torch.bfloat16).cuda(), w, out=rnd((9, N), 4, torch.float32).cuda(),
+        k.gemm_skinny(rnd((17, K), 1, torch.bfloat16).cuda(), w, out=rnd((17, N), 4, torch.float32).cuda(),
                       accumulate=True, emit=k.NormEmit(nw))
     with pytest.raises(k.KernelError):
         k.gemm_skinny(a, w, out=res.bfloat16(), accumulate=True, emit=k.NormEmit(nw))
@@ -389,8 +390,9 @@ def test_gemm_skinny_conv_equals_the_unfused_step(k, M, D, K, taps, bias, norm):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
     """A row's contraction is the same bits alone, in a batch, and at another place of it, as long
-    as the same kernel runs: in float32 always; in bfloat16 among batches of up to 8 rows (the
-    mma.sync kernel) and among batches of 9 to 64 rows (the tcgen05 kernel with split K)."""
+    as the same kernel runs: in float32 always; in bfloat16 among batches of up to 16 rows (the
+    mma.sync kernel, whose warps split K the same way for 8 and for 16 rows) and among batches of 17
+    to 64 rows (the tcgen05 kernel with split K)."""
     from zinfer_b200.parts.linear import linear
     a = rnd((70, 96), 9, dtype).cuda()
     w = rnd((200, 96), 10, dtype, 0.1).cuda()
@@ -403,11 +405,12 @@ def test_linear_rows_do_not_depend_on_the_batch(k, dtype):
     small = linear(a[28:36].contiguous(), w, out_dtype=torch.float32)            # 8 rows
     one = linear(a[33:34].contiguous(), w, out_dtype=torch.float32)
     moved = linear(a[30:35].contiguous(), w, out_dtype=torch.float32)
-    assert torch.equal(small[5], one[0]) and torch.equal(small[5], moved[3])
+    more = linear(a[22:38].contiguous(), w, out_dtype=torch.float32)             # 16 rows
+    assert torch.equal(small[5], one[0]) and torch.equal(small[5], moved[3]) and torch.equal(small[5], more[11])
     wide = rnd((2048, 96), 11, dtype, 0.1).cuda()                               # enough rows for a split of K
     big = linear(a[:64].contiguous(), wide, out_dtype=torch.float32)
     mid = linear(a[20:40].contiguous(), wide, out_dtype=torch.float32)          # 20 rows
-    few = linear(a[30:39].contiguous(), wide, out_dtype=torch.float32)          # 9 rows
+    few = linear(a[30:47].contiguous(), wide, out_dtype=torch.float32)          # 17 rows
     assert torch.equal(big[33], mid[13]) and torch.equal(big[33], few[3])
 
 

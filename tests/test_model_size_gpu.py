@@ -4,7 +4,7 @@ engine and the plain implementation from the same file.
 
 At this size the engine takes kernels that no tiny configuration reaches: pairs of thread blocks
 on 256 x 256 tiles with the TMA reduce-add into the residual stream, the SwiGLU epilogue of the
-tcgen05 product with the weights on its 128-row side (9 to 64 rows and 2F > 12,288 only), its
+tcgen05 product with the weights on its 128-row side (17 to 64 rows and 2F > 12,288 only), its
 split-K over a cluster of 8 blocks, 32 heads on 8 KV heads in the tcgen05 prompt attention, a
 head of 65,536 rows.
 
@@ -27,7 +27,7 @@ pytestmark = pytest.mark.gpu
 
 VOCAB = LFM2_1_2B["vocab_size"]
 TAIL = 32
-# requests: three of 40 / 129 / 300 tokens, and twenty short ones for batches of 9 to 64 rows
+# requests: three of 40 / 129 / 300 tokens, and twenty short ones for batches of 9 to 64 rows (both kernels for few rows)
 LENS = [40, 129, 300] + [5 + (7 * i) % 56 for i in range(20)]
 BATCHES = [[0, 1, 2], list(range(3, 23)), [2, 0, 22, 1]]
 

@@ -82,8 +82,15 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 // RG: groups of 16 weight rows per block; NT: groups of 8 tokens; UNROLL: 32-wide k slabs whose
 // weight loads are in flight together.  N is the number of output columns; for EPI_PLAIN weight
 // row = column, for the fused epilogues block b holds weight rows b*16*RG .. (interleaved parts).
+// Blocks per SM asked of the compiler for the variants of 9 to 16 rows (two groups of 8 tokens): left to
+// itself it gave the 8-warp ones 138 registers (one block per SM where two fit with 128) and held the
+// 16-warp ones to 74 (few loads in flight).  Measured at 16 rows on the LFM2-1.2B shapes: w1|w3 21.3 ->
+// 16.4 us, w2 14.1 -> 9.0, qkv 8.0 -> 5.9, out_proj 3.9 -> 3.1.  The variants of up to 8 rows lose with
+// such a bound (a step of 8 rows 0.668 -> 0.724 ms) and keep the compiler's own choice.
+constexpr int skinny_min_blocks(int warps, int nt, int epi) { return nt == 2 ? (warps == 8 && epi == EPI_PLAIN ? 2 : 1) : 0; }
+
 template <int WARPS, int RG, int NT, int UNROLL, int EPI, int NORM_MODE, typename TC, bool EMIT = false>
-__global__ void __launch_bounds__(WARPS * 32) skinny_kernel(const Args a) {
+__global__ void __launch_bounds__(WARPS * 32, skinny_min_blocks(WARPS, NT, EPI)) skinny_kernel(const Args a) {
   constexpr bool NORM = NORM_MODE == NORM_FUSED;   // the prologue that normalises float32 rows
   extern __shared__ float smem[];
   constexpr int RED_LD = NT * 8 + 1;
@@ -473,6 +480,13 @@ int dispatch_plain(const Args& a, cudaStream_t stream) {
     return launch<8, 1, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
   }
   if (a.M <= 16) {
+    if constexpr (NORM_MODE == NORM_NONE && std::is_same<TC, float>::value) {
+      if (a.emit_x) {
+        if (few) return launch<16, 1, 2, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
+        if (many) return launch<8, 2, 2, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
+        return launch<8, 1, 2, 4, EPI_PLAIN, NORM_NONE, TC, true>(a, stream);
+      }
+    }
     if (few) return launch<16, 1, 2, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
     if (many) return launch<8, 2, 2, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
     return launch<8, 1, 2, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
@@ -530,7 +544,7 @@ int zk_gemm_skinny_fused_max_m() { return 16; }
 // X [M, K] bfloat16 (or Xf [M, K] float32 + norm_w [K], eps: RMSNorm fused, M <= 16), W [N, K]
 // bfloat16 with K % 8 == 0 and 16-byte aligned rows; C [M, N] bfloat16 or float32.
 // ssq_in [M, ssq_parts] (or null): X is bfloat16(x * norm weight) and the sums are scaled by
-// 1 / sqrt(sum(ssq_in[m]) / K + eps) (M <= 16).  emit_x (or null; M <= 8, float32 C, no fused norm):
+// 1 / sqrt(sum(ssq_in[m]) / K + eps) (M <= 16).  emit_x (or null; M <= 16, float32 C, no fused norm):
 // also writes emit_x [M, N] = bfloat16(C * emit_w) and emit_ssq [M, ceil(N / 16)] for the next norm.
 int zk_gemm_skinny(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* C,
                    const float* bias, int M, int N, int K, int ldx, int ldw, int ldc, int out_dtype, int accumulate,
@@ -543,7 +557,7 @@ int zk_gemm_skinny(const void* X, const float* Xf, const float* norm_w, float ep
   a.ssq_in = Xf ? nullptr : ssq_in; a.ssq_parts = ssq_parts;
   a.emit_w = emit_w; a.emit_x = (bf16*)emit_x; a.emit_ssq = emit_ssq;
   if (ldc < N || check_common(a, Xf ? 16 : 64)) return ZK_EINVAL;
-  if (emit_x && (!emit_w || !emit_ssq || M > 8 || Xf || out_dtype != ZK_F32)) return ZK_EINVAL;
+  if (emit_x && (!emit_w || !emit_ssq || M > 16 || Xf || out_dtype != ZK_F32)) return ZK_EINVAL;
   if (out_dtype == ZK_F32) return dispatch_plain_any<float>(a, stream);
   if (out_dtype == ZK_BF16) return dispatch_plain_any<bf16>(a, stream);
   return ZK_EINVAL;

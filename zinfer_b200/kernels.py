@@ -411,7 +411,7 @@ class NormEmit:
         self.ssq: Optional[torch.Tensor] = None
 
 
-GEMM_SKINNY_EMIT_MAX_M = 8
+GEMM_SKINNY_EMIT_MAX_M = 16
 
 
 def _skinny_input(a):
@@ -474,7 +474,7 @@ def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtyp
         _need(bias, "bias", torch.float32, (N,))
     if emit is not None:
         if not gemm_skinny_emits(a, out):
-            raise KernelError("gemm_skinny: the norm's inputs are written for at most 8 bfloat16 rows "
+            raise KernelError("gemm_skinny: the norm's inputs are written for at most 16 bfloat16 rows "
                               "summed into contiguous float32 rows")
         _need(emit.weight, "norm weight", torch.float32, (N,))
         emit.xw = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)

@@ -48,7 +48,7 @@ class SwiGLU(FeedForward):
                 if not kernels.gemm_tc_takes(x, w):
                     x = as_tensor(xn)
                 rows = x.shape[0]
-                # prompt steps, and steps of 9..64 rows: activation in the epilogue
+                # prompt steps, and steps of 17..64 rows: activation in the epilogue
                 if (rows > kernels.gemm_skinny_max_m() or tc_rows) and kernels.gemm_tc_takes(x, w):
                     splits = swapped_splits(w.shape[0], kernels.sm_count(w.device)) if tc_rows else 1
                     h = kernels.gemm_tc(x, w, swiglu=True, splits=splits)

@@ -9,12 +9,14 @@ from __future__ import annotations
 from .. import kernels
 
 
-# Between 9 and 64 rows the tcgen05 kernel with the weights on its 128-row side beats the mma.sync
+# From 17 to 64 rows the tcgen05 kernel with the weights on its 128-row side beats the mma.sync
 # kernel (measured at 64 rows on the LFM2-1.2B shapes: 17 us against 44 us for N = 16384, 10 against
-# 22 for N = 6144, 7 against 12 for N = 2048, 12 against 38 for N = 2048 with K = 8192; a whole step
-# of 9 sequences 0.97 against 1.13 ms, of 16 sequences 1.15 against 1.31 ms); up to 8 rows the
-# mma.sync kernel is as fast or faster.
-TC_SWAPPED_MIN_ROWS = 9
+# 22 for N = 6144, 7 against 12 for N = 2048, 12 against 38 for N = 2048 with K = 8192).  Up to 16
+# rows the mma.sync kernel is as fast or faster (16 rows: 3.1 against 5.0 us for out_proj, 9.0
+# against 10.3 for w2, 5.9 against 6.1 for qkv, 9.3 against 8.6 for in_proj, 16.4 against 15.7 for
+# w1|w3), fuses the short convolution and needs no cluster: whole steps of 9 / 12 / 16 sequences
+# 0.83 / 0.84 / 0.88 ms against 0.90 / 0.91 / 0.97.
+TC_SWAPPED_MIN_ROWS = 17
 
 
 def swapped_splits(n_weight_rows: int, sm_count: int) -> int:
