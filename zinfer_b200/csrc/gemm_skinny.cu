@@ -463,6 +463,9 @@ int dispatch_plain(const Args& a, cudaStream_t stream) {
   // are requested at once (128 registers a thread, one block per SM).  Measured on whole steps of the
   // LFM2-1.2B shape, whose w2 has K = 8192: 0.5810 -> 0.5728 ms at one row, 0.7015 -> 0.6945 ms at 8.
   const bool long_k = a.K >= 4096;
+  // one_wave: more 16-row blocks than SMs but at most two per SM (qkv of the LFM2-1.2B shape: 192).  Blocks
+  // of 16 warps take an SM each and run in two rounds; blocks of 8 warps with 8 slabs in flight are all
+  // resident at once.  Measured on whole steps: 0.5714 -> 0.5604 ms at one row, 0.681 -> 0.670 ms at 8.
   if (a.M <= 8) {
     if constexpr (NORM_MODE == NORM_NONE && std::is_same<TC, float>::value) {
       if (a.emit_x) {
@@ -475,6 +478,7 @@ int dispatch_plain(const Args& a, cudaStream_t stream) {
     if constexpr (NORM_MODE == NORM_NONE) {
       if (few && long_k) return launch<16, 1, 1, 8, EPI_PLAIN, NORM_NONE, TC>(a, stream);
     }
+    if (few && a.N > 16 * 148) return launch<8, 1, 1, 8, EPI_PLAIN, NORM_MODE, TC>(a, stream);   // see one_wave above
     if (few) return launch<16, 1, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
     if (many) return launch<8, 2, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
     return launch<8, 1, 1, 4, EPI_PLAIN, NORM_MODE, TC>(a, stream);
