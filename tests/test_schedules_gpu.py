@@ -1,6 +1,6 @@
 """Schedules of the engine that only large or long batches reach, against the plain implementation:
-single-token steps of 12, 20 and 40 sequences whose batch shrinks as requests end (the kernels
-chosen for up to 8, up to 16 and up to 64 rows, each recorded in a CUDA graph and replayed), a
+single-token steps of 12, 20, 40 and 100 sequences whose batch shrinks as requests end (the kernels
+chosen for up to 8, up to 16, up to 64 and more than 64 rows, each recorded in a CUDA graph and replayed), a
 second batch in the same engine; sequences that grow past 512, 768 and 1024 tokens, where the
 layout of the key chunks of single-token attention (and with it the recorded step) changes;
 and prompts cut into chunks of 64 and 128 tokens in bfloat16.  All on the loud configurations,
@@ -52,7 +52,7 @@ def drive(engine, seqs, heads, ref, use_decode=True):
     return worst, where, sizes
 
 
-@pytest.mark.parametrize("n_seqs,dtype", [(12, "bfloat16"), (20, "bfloat16"), (40, "bfloat16"), (20, "float32")])
+@pytest.mark.parametrize("n_seqs,dtype", [(12, "bfloat16"), (20, "bfloat16"), (40, "bfloat16"), (20, "float32"), (100, "bfloat16")])
 @pytest.mark.parametrize("name", ["loud_d", "loud_e"])
 def test_many_sequences_shrinking_batches_then_a_second_batch(model_folders, name, n_seqs, dtype):
     import zinfer_b200 as z
