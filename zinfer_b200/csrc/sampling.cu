@@ -309,9 +309,16 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
   return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)idx);
 }
 
+// `ring`, if given, holds [ring_slots][n + 1] words: the finalising block also writes the tokens and the
+// status word into slot (*ring_pos % ring_slots) and adds one to *ring_pos.  The host, which counts the
+// launches too, can then fetch a step's result from its slot on another stream while later steps
+// (recorded with the same pointers) run on and fill other slots: no copy has to be queued between two
+// steps.  (Pinned host memory as the ring works too, but a kernel that ends on writes to the host held
+// up the step behind it by some 25 us.)
 __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out, int* __restrict__ feed,
                               const int* __restrict__ status, unsigned long long* __restrict__ keys,
-                              unsigned* __restrict__ counter) {
+                              unsigned* __restrict__ counter, int* __restrict__ ring, int ring_slots,
+                              unsigned* __restrict__ ring_pos) {
   __shared__ Shared sh;
   __shared__ int sm_last;
   zk_let_next_start();
@@ -339,15 +346,23 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
   __syncthreads();
   if (sm_last) {
     __threadfence();
+    int* slot = ring ? ring + (size_t)(*ring_pos % (unsigned)ring_slots) * (n + 1) : nullptr;
     for (int r = threadIdx.x; r < n; r += blockDim.x) {
       const unsigned long long k = __ldcg(keys + r);
       const int tok = k ? (int)(0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull)) : 0;
       out[r] = tok;
       if (feed) feed[r] = tok;
+      if (slot) slot[r] = tok;
       keys[r] = 0ull;
     }
+    __syncthreads();     // every thread has read *ring_pos
     if (threadIdx.x == 0) {
-      if (status) out[n] = *status;
+      const int st = status ? *status : 0;
+      if (status) out[n] = st;
+      if (slot) {
+        slot[n] = st;
+        *ring_pos = *ring_pos + 1u;
+      }
       *counter = 0u;
     }
   }
@@ -795,15 +810,18 @@ int zk_recent_append(const int* tokens, int n, int* recent, int* seen, const int
 
 // out [n] (or [n + 1] with `status`: out[n] = *status); feed [n] or null.  `scratch` holds n 64-bit keys
 // and, behind them, one 32-bit counter, all zero before the launch and again after it.
+// ring (or null): [ring_slots][n + 1] words, see the kernel; ring_pos: one device word, the number of
+// launches with a ring so far.
 int zk_argmax(const float* logits, int n, int V, int* out, int* feed, const int* status, void* scratch,
-              cudaStream_t stream) {
+              int* ring, int ring_slots, int* ring_pos, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (V <= 0 || !scratch) return ZK_EINVAL;
+  if (V <= 0 || !scratch || (ring && (ring_slots <= 0 || !ring_pos))) return ZK_EINVAL;
   // a few SMs' worth of blocks per step: a row of 65,536 logits is cut into 16 pieces
   const int pieces = V >= 16384 ? 16 : (V >= 4096 ? 4 : 1);
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(scratch);
   return zk_launch_dependent(argmax_kernel, dim3(n, pieces), dim3(256), 0, stream, logits, V, out, feed, status, keys,
-                             reinterpret_cast<unsigned*>(keys + n));
+                             reinterpret_cast<unsigned*>(keys + n), ring, ring_slots,
+                             reinterpret_cast<unsigned*>(ring_pos));
 }
 
 // uniforms [n, 2], or null and then seed, req_ids [n] (the request of each row; distinct) and

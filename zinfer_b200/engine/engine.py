@@ -49,6 +49,7 @@ class _DecodeBatch:
     that runs several steps ahead of the device cannot change a step's input under it."""
 
     RING = 4
+    OUT_RING = 4        # results the host may still have to read while later steps run (it reads one step late)
 
     def __init__(self, n_seqs: int, vocab: int, device):
         words = batch_layout(n_seqs, n_seqs)["_total"][0]
@@ -56,6 +57,13 @@ class _DecodeBatch:
         self.logits = torch.empty((n_seqs, vocab), dtype=torch.float32, device=device)
         # every step ends with the arg-max of its logits: the n tokens and, behind them, the status word
         self.greedy = torch.zeros(n_seqs + 1, dtype=torch.int32, device=device)
+        # ... and writes both into slot (step % OUT_RING) of a ring as well, the device counting the steps in
+        # `ring_pos` as the host does in `steps`: the host fetches a step's slot on a stream of its own
+        # while the next step runs.  The same copy queued between two recorded steps cost 40 us a step.
+        self.ring = torch.zeros((self.OUT_RING, n_seqs + 1), dtype=torch.int32, device=device)
+        self.host_ring = torch.zeros((self.OUT_RING, n_seqs + 1), dtype=torch.int32).pin_memory()
+        self.ring_pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.steps = 0
         self.n_seqs = n_seqs
         self._tail = batch_layout(n_seqs, n_seqs)["tok_seq"][0]      # where the description goes on behind the token ids
         self._hosts = [torch.zeros(words, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
@@ -141,6 +149,7 @@ class Engine:
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self.graph_captures = 0         # steps that were recorded instead of replayed, since the engine was built
         self._host_ring, self._host_next = None, 0      # pinned buffers the sampled tokens are read into
+        self._copy_stream = None                        # the stream on which recorded steps' tokens are fetched
         self.interrupt = threading.Event()   # set it (from a signal handler, another thread, a callback) to end `generate`
         self.stats = None
 
@@ -295,7 +304,8 @@ class Engine:
         `batch.greedy` (with the status word behind it: one small copy brings both to the host) and into
         the token slots of the batch description, where the next step of the same batch finds it."""
         self.model.forward(ctx, self.calls, None, want_all=True, out=batch.logits)
-        kernels.argmax(batch.logits, out=batch.greedy, feed=batch.meta_dev[:batch.n_seqs], status=self.status)
+        kernels.argmax(batch.logits, out=batch.greedy, feed=batch.meta_dev[:batch.n_seqs], status=self.status,
+                       ring=batch.ring, ring_pos=batch.ring_pos)
 
     def greedy_tokens(self, logits: torch.Tensor) -> Optional[torch.Tensor]:
         """If `logits` are what the last `decode` returned from a recorded (or warm-up) step: the int32
@@ -307,9 +317,30 @@ class Engine:
                 return batch.greedy
         return None
 
+    def read_greedy_async(self, logits: torch.Tensor):
+        """For logits that the last `decode` returned: an object whose `wait()` gives the arg-max tokens
+        of that step on the host (and raises on a device status).  The step's last kernel left them in a
+        slot of the batch's ring; they are copied from there on a stream of their own, so the steps that
+        follow on the main stream do not wait for the copy.  None for logits of any other origin."""
+        for batch in self._decode_batches.values():
+            if batch.logits is logits:
+                slot = (batch.steps - 1) % batch.OUT_RING
+                ran = torch.cuda.Event()
+                ran.record()
+                if self._copy_stream is None:
+                    self._copy_stream = torch.cuda.Stream(device=self.device)
+                done = torch.cuda.Event()
+                with torch.cuda.stream(self._copy_stream):
+                    self._copy_stream.wait_event(ran)
+                    batch.host_ring[slot].copy_(batch.ring[slot], non_blocking=True)
+                    done.record()
+                return _PendingTokens(self, batch.host_ring[slot], done)
+        return None
+
     def _decode_graph(self, batch: _DecodeBatch, B: int, longest: int) -> torch.Tensor:
         ctx = StepContext(self.dtype, self.device, self.status, batch.meta_dev, B, B, [1] * B, longest,
                           memo=batch.memo, sm_count=self.sm_count)
+        batch.steps += 1            # the kernels run once below (a recording in between runs nothing)
         if not batch.warmed:
             batch.warmed = True
             self._forward_single_tokens(ctx, batch)
@@ -377,18 +408,31 @@ class Engine:
     def read_tokens_async(self, tokens: torch.Tensor, with_status: bool = False):
         """Starts copying sampled tokens (and the status word) to the host; the returned object's
         `wait()` gives them once the copy has run, whatever was launched after it.  `with_status`: the
-        tensor's last element already is the status word (`greedy_tokens`)."""
-        both = tokens if with_status else torch.cat([tokens.to(torch.int32), self.status])
+        tensor's last element already is the status word (`greedy_tokens`).  The copy runs on a stream of
+        its own behind what has been launched so far: queued on the main stream it would stand between
+        two steps and cost them 40 us.  `tokens` must not be written again before `wait()` returns."""
         ring = self._host_ring
-        if ring is None or ring[0].numel() < both.numel():
-            ring = self._host_ring = [torch.empty(max(both.numel(), self.cache.max_slots + 1), dtype=torch.int32,
+        n = tokens.numel() + (0 if with_status else 1)
+        if ring is None or ring[0].numel() < n:
+            ring = self._host_ring = [torch.empty(max(n, self.cache.max_slots + 1), dtype=torch.int32,
                                                   pin_memory=True) for _ in range(8)]
         self._host_next = (self._host_next + 1) % len(ring)
-        host = ring[self._host_next][:both.numel()]     # at most two reads are under way at a time
-        host.copy_(both, non_blocking=True)
+        host = ring[self._host_next][:n]     # at most two reads are under way at a time
+        ran = torch.cuda.Event()
+        ran.record()
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
         done = torch.cuda.Event()
-        done.record()
-        return _PendingTokens(self, host, done)
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(ran)
+            m = tokens.numel()
+            host[:m].copy_(tokens if tokens.dtype == torch.int32 else tokens.to(torch.int32), non_blocking=True)
+            if not with_status:
+                host[m:].copy_(self.status, non_blocking=True)
+            done.record()
+        pending = _PendingTokens(self, host, done)
+        pending.source = tokens          # alive until the copy has run
+        return pending
 
     def generate(self, prompts, max_new_tokens: int = 256, sampling=None, stop_ids=None, on_step=None,
                  **sampling_options):

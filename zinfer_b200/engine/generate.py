@@ -208,7 +208,10 @@ class GenerationLoop:
                 packed = greedy(logits) if greedy is not None else None
                 if packed is not None:      # the step computed its own arg-max; the status word lies behind it
                     nxt_dev = packed[:len(ahead)]
-                    nxt_pending = be.read_tokens_async(packed, with_status=True)
+                    direct = getattr(be, "read_greedy_async", None)      # ... and may have written both to the host
+                    nxt_pending = direct(logits) if direct is not None else None
+                    if nxt_pending is None:
+                        nxt_pending = be.read_tokens_async(packed, with_status=True)
                 else:
                     nxt_dev = sampler.sample(logits, ahead)
                     nxt_pending = be.read_tokens_async(nxt_dev)

@@ -75,7 +75,7 @@ _SIGNATURES = {
         "zk_recent_window": "",
         "zk_penalize_recent": "piipppfp",
         "zk_recent_append": "pipppp",
-        "zk_argmax": "piippppp",
+        "zk_argmax": "piipppp" + "pip" + "p",
         "zk_sample": "piififfffip" + "lpp" + "pp",
     },
     "attention": {
@@ -804,12 +804,20 @@ def recent_append(tokens, recent, seen, req_ids) -> None:
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed: Optional[torch.Tensor] = None,
-           status: Optional[torch.Tensor] = None) -> torch.Tensor:
+           status: Optional[torch.Tensor] = None, ring: Optional[torch.Tensor] = None,
+           ring_pos: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Lowest index among the largest logits of each row; int32 [n].  `out` may be given (with
     `status` it has n + 1 words and the last receives the status word's value); `feed` [n] receives
-    the same indices (the next step's token slots)."""
+    the same indices (the next step's token slots).  `ring` int32 [slots, n + 1]: the kernel also
+    writes the tokens and the status word into slot (ring_pos % slots) and adds one to `ring_pos`
+    (one int32 word on the device), so that a step's result stays where it is while later steps run."""
     _need(logits, "logits", torch.float32, (None, None))
     n, V = logits.shape
+    ring_slots = 0
+    if ring is not None:
+        _need(ring, "ring", torch.int32, (None, n + 1))
+        _need(ring_pos, "ring_pos", torch.int32, (1,))
+        ring_slots = ring.shape[0]
     if out is None:
         out = torch.empty(n + (1 if status is not None else 0), dtype=torch.int32, device=logits.device)
     _need(out, "out", torch.int32, (n + (1 if status is not None else 0),))
@@ -819,7 +827,7 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed: Optio
         _need(status, "status", torch.int32)
     scratch = _argmax_scratch(logits.device, n)
     _check(_fn("sampling", "zk_argmax")(_ptr(logits), n, V, _ptr(out), _ptr(feed), _ptr(status), _ptr(scratch),
-                                        _stream()), "argmax")
+                                        _ptr(ring), ring_slots, _ptr(ring_pos), _stream()), "argmax")
     return out
 
 
